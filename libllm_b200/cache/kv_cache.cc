@@ -129,8 +129,11 @@ void KVCache::commit(int slot, int new_len) {
   rec.length = new_len;
   for (size_t g = 0; g < groups_.size(); ++g) {
     const CacheNeed &need = groups_[g].need;
-    if (need.kind != "window" || need.window <= 0) continue;
-    const int first_needed = std::max(0, new_len - need.window + 1);
+    int first_needed = 0;
+    if (need.kind == "window" && need.window > 0) first_needed = std::max(0, new_len - need.window + 1);
+    // a query at position p >= new_len sees no key before the start of its own block
+    else if (need.kind == "block" && need.block > 0) first_needed = new_len / need.block * need.block;
+    else continue;
     std::vector<int> drop;
     const int upto = std::min(first_needed / page_size_, (int)rec.pages[g].size());
     for (int lp = 0; lp < upto; ++lp)
@@ -222,6 +225,7 @@ Json KVCache::info() const {
     g.set("k_dim", grp.need.k_dim);
     g.set("v_dim", grp.need.v_dim);
     g.set("window", grp.need.window > 0 ? Json(grp.need.window) : Json());
+    g.set("block", grp.need.block > 0 ? Json(grp.need.block) : Json());
     g.set("runs", Json::list(grp.runs));
     g.set("pages_in_use", grp.pool->in_use());
     g.set("pages_available", grp.pool->available());

@@ -6,7 +6,7 @@
 // [runs, pages, kv_heads, page_size, k_dim] and V likewise with v_dim (no V when v_dim is 0).
 // A sequence holds, per group, a list mapping its logical pages (position / page_size) to pool
 // pages; a "window" group gives pages back as soon as every position in them has left the
-// window.  The reference keeps one growing tensor pair per layer for one rectangular batch
+// window, a "block" group as soon as the sequence has grown past their block.  The reference keeps one growing tensor pair per layer for one rectangular batch
 // (src/libllm/kv_cache.h:31-59, src/libllm/llama.cc:188-212).
 #pragma once
 #include <map>
@@ -62,8 +62,8 @@ class KVCache {
   // Pages for every sequence of `growth` (slot, new length).  Either all are granted or
   // Error(Cache) is thrown and nothing has changed.
   void reserve(const std::vector<std::pair<int, int>> &growth);
-  // The sequence now holds new_len tokens; window groups drop pages no later query can see (a
-  // query at position p >= new_len sees keys > p - window).
+  // The sequence now holds new_len tokens; window and block groups drop pages no later query can
+  // see (a query at position p >= new_len sees keys > p - window, or keys from the start of p's block).
   void commit(int slot, int new_len);
   // int32 [slots.size(), width] into `out`; unused entries are 0 (never read: positions beyond a
   // sequence's length are never asked for) and released ones -1.

@@ -137,6 +137,7 @@ LLM_API int32_t llm_part_describe(llm_part_t *p, llm_json_t *out) {
         cj.set("k_dim", c.k_dim);
         cj.set("v_dim", c.v_dim);
         cj.set("window", c.window > 0 ? Json(c.window) : Json());
+        cj.set("block", c.block > 0 ? Json(c.block) : Json());
         j.set("cache", cj);
       } else {
         j.set("cache", Json());

@@ -74,7 +74,7 @@ std::mutex &table_lock() {
 }
 }  // namespace
 
-void register_builtin_architectures();   // config/llama.cc
+void register_builtin_architectures();   // config/llama.cc, which calls the other files' own
 void register_architecture_unlocked(Architecture arch) { table()[arch.name] = std::move(arch); }
 
 static void ensure_builtin() {
@@ -126,17 +126,20 @@ Json read_config_json(const std::string &folder) {
   return data;
 }
 
+std::string architecture_name(const Json &config_json, const std::string &where) {
+  if (config_json.is_object())
+    for (const char *key : {"model_type", "architecture"})
+      if (config_json.get(key).is_string()) return config_json.get(key).as_string();
+  LLM_THROW(Config, "%s: required key 'model_type' is missing", where.c_str());
+}
+
 Json parse_config(const Json &config_json) {
-  if (!config_json.is_object() || !config_json.get("model_type").is_string())
-    LLM_THROW(Config, "config.json: required key 'model_type' is missing");
-  return architecture_for(config_json.get("model_type").as_string()).parse(config_json);
+  return architecture_for(architecture_name(config_json, "config.json")).parse(config_json);
 }
 
 Json load_config(const std::string &folder) {
   const Json data = read_config_json(folder);
-  if (!data.get("model_type").is_string())
-    LLM_THROW(Config, "%s/config.json: required key 'model_type' is missing", folder.c_str());
-  return architecture_for(data.get("model_type").as_string()).parse(data);
+  return architecture_for(architecture_name(data, folder + "/config.json")).parse(data);
 }
 
 }  // namespace llm

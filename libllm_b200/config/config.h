@@ -58,6 +58,8 @@ std::vector<std::string> known_architectures();
 // src/libllm/model_for_generation.cc:47-49).
 const Architecture &architecture_for(const std::string &model_type);
 
+// The name a config.json picks its architecture by: its `model_type`, or else its `architecture`.
+std::string architecture_name(const Json &config_json, const std::string &where);
 Json read_config_json(const std::string &folder);
 // config.json of `folder` in its architecture's normal form.
 Json load_config(const std::string &folder);

@@ -185,6 +185,8 @@ void register_builtin_architectures() {
   // straight into the table: register_architecture() would wait for this very call to finish
   extern void register_architecture_unlocked(Architecture);
   register_architecture_unlocked(std::move(a));
+  extern void register_sinezen_architecture();     // config/sinezen.cc
+  register_sinezen_architecture();
 }
 
 }  // namespace llm

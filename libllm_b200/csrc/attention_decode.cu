@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(AD_THREADS)
 attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
                         const __nv_bfloat16 *__restrict__ kc, const __nv_bfloat16 *__restrict__ vc,
                         const int *__restrict__ tok_pos, const int *__restrict__ page_table, int pt_stride,
-                        int n_kv, int page_size, int chunk, int window, float scale_log2,
+                        int n_kv, int page_size, int chunk, int window, int block, float scale_log2,
                         float *__restrict__ ws_o, float *__restrict__ ws_ml, int n_splits,
                         __nv_bfloat16 *__restrict__ out, long long out_stride) {
   constexpr int LPK = D / 8;                 // lanes per key
@@ -53,7 +53,7 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
   grid_dependents_launch();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int len = tok_pos[b] + 1;
-  const int kstart = window > 0 ? max(0, len - window) : 0;
+  const int kstart = max(window > 0 ? max(0, len - window) : 0, block > 0 ? (len - 1) / block * block : 0);
   const int c0 = split * chunk;
   const int c1 = min(c0 + chunk, len);
   if (c0 >= len || c1 <= kstart) {
@@ -230,13 +230,13 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
 // Joins the splits of one (sequence, head): out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
 __global__ void attention_decode_combine_kernel(const float *__restrict__ ws_o, const float *__restrict__ ws_ml,
                                                 const int *__restrict__ tok_pos, int n_heads, int D, int chunk,
-                                                int window, int n_splits, __nv_bfloat16 *__restrict__ out,
+                                                int window, int block, int n_splits, __nv_bfloat16 *__restrict__ out,
                                                 long long out_stride) {
   grid_dependents_launch();
   grid_dependency_wait();
   const int head = blockIdx.x, b = blockIdx.y;
   const int len = tok_pos[b] + 1;
-  const int kstart = window > 0 ? max(0, len - window) : 0;
+  const int kstart = max(window > 0 ? max(0, len - window) : 0, block > 0 ? (len - 1) / block * block : 0);
   // Splits beyond n_splits do not exist (the caller's n_splits * chunk should cover the longest
   // sequence; keys beyond it were not attended to): never read another head's scratch.
   const int first = min(kstart / chunk, n_splits - 1), last = min((len - 1) / chunk, n_splits - 1);
@@ -255,20 +255,20 @@ __global__ void attention_decode_combine_kernel(const float *__restrict__ ws_o, 
 template <int D, int G>
 static int launch_decode(const void *q, long long q_stride, const void *kc, const void *vc, const int *tok_pos,
                          const int *page_table, int pt_stride, int n_seqs, int n_kv, int page_size, int chunk,
-                         int n_splits, int window, float scale, float *ws_o, float *ws_ml, void *out,
+                         int n_splits, int window, int block, float scale, float *ws_o, float *ws_ml, void *out,
                          long long out_stride, cudaStream_t stream) {
   dim3 grid(n_splits, n_kv, n_seqs);
   const size_t smem = (size_t)((chunk + page_size - 1) / page_size) * sizeof(int);
   LLM_REQUIRE(smem <= 16 * 1024, "attention_decode: a chunk of %d keys spans too many pages", chunk);
   llm_launch(attention_decode_kernel<D, G>, grid, dim3(AD_THREADS), smem, stream,
       (const __nv_bfloat16 *)q, q_stride, (const __nv_bfloat16 *)kc, (const __nv_bfloat16 *)vc, tok_pos, page_table,
-      pt_stride, n_kv, page_size, chunk, window, scale * 1.4426950408889634f, ws_o, ws_ml, n_splits,
+      pt_stride, n_kv, page_size, chunk, window, block, scale * 1.4426950408889634f, ws_o, ws_ml, n_splits,
       (__nv_bfloat16 *)out, out_stride);
   LLM_CHECK_LAUNCH("attention_decode");
   if (n_splits > 1) {
     dim3 cgrid(n_kv * G, n_seqs);
     llm_launch(attention_decode_combine_kernel, cgrid, dim3(D < 64 ? 32 : 64), 0, stream, (const float *)ws_o,
-               (const float *)ws_ml, tok_pos, n_kv * G, D, chunk, window, n_splits, (__nv_bfloat16 *)out, out_stride);
+               (const float *)ws_ml, tok_pos, n_kv * G, D, chunk, window, block, n_splits, (__nv_bfloat16 *)out, out_stride);
     LLM_CHECK_LAUNCH("attention_decode_combine");
   }
   return LLM_OK;
@@ -287,7 +287,7 @@ LLM_EXPORT int llm_attention_decode_supports(int d, int group) {
 LLM_EXPORT int llm_attention_decode(const void *q, long long q_stride, void *out, long long out_stride,
                                     const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                                     int pt_stride, int n_seqs, int n_heads, int n_kv, int d, int page_size,
-                                    int chunk, int n_splits, int window, float scale, float *ws_o, float *ws_ml,
+                                    int chunk, int n_splits, int window, int block, float scale, float *ws_o, float *ws_ml,
                                     cudaStream_t stream) {
   if (n_seqs == 0) return LLM_OK;
   LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_kv > 0 && n_kv <= 65535 && n_heads % n_kv == 0, "attention_decode: bad sizes");
@@ -299,7 +299,7 @@ LLM_EXPORT int llm_attention_decode(const void *q, long long q_stride, void *out
 #define AD_CASE(DD, GG)                                                                                         \
   if (d == DD && group == GG)                                                                                   \
     return launch_decode<DD, GG>(q, q_stride, kc, vc, tok_pos, page_table, pt_stride, n_seqs, n_kv, page_size, \
-                                 chunk, n_splits, window, scale, ws_o, ws_ml, out, out_stride, stream);
+                                 chunk, n_splits, window, block, scale, ws_o, ws_ml, out, out_stride, stream);
 #define AD_CASES(DD) AD_CASE(DD, 1) AD_CASE(DD, 2) AD_CASE(DD, 3) AD_CASE(DD, 4) AD_CASE(DD, 8)
   AD_CASES(16) AD_CASES(32) AD_CASES(64) AD_CASES(128)
 #undef AD_CASES
@@ -339,7 +339,7 @@ LLM_EXPORT long long llm_attention_decode_static_floats_needed(int n_seqs, int n
 LLM_EXPORT int llm_attention_decode_static(const void *q, long long q_stride, void *out, long long out_stride,
                                            const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                                            int pt_stride, int n_seqs, int n_heads, int n_kv, int d, int page_size,
-                                           int chunk, int n_splits, int window, float scale, cudaStream_t stream) {
+                                           int chunk, int n_splits, int window, int block, float scale, cudaStream_t stream) {
   if (n_seqs == 0) return LLM_OK;
   LLM_REQUIRE(n_seqs > 0 && n_heads > 0 && d > 0 && n_splits >= 1, "attention_decode_static: bad sizes");
   const long long need = llm_attention_decode_static_floats_needed(n_seqs, n_heads, d, n_splits);
@@ -367,5 +367,5 @@ LLM_EXPORT int llm_attention_decode_static(const void *q, long long q_stride, vo
     ws_ml = base + (size_t)n_seqs * n_heads * n_splits * d;
   }
   return llm_attention_decode(q, q_stride, out, out_stride, kc, vc, tok_pos, page_table, pt_stride, n_seqs, n_heads, n_kv,
-                              d, page_size, chunk, n_splits, window, scale, ws_o, ws_ml, stream);
+                              d, page_size, chunk, n_splits, window, block, scale, ws_o, ws_ml, stream);
 }

@@ -13,7 +13,7 @@ extern "C" {
 // attended to.  Returns 0 or a status; llm_attention_decode_last_error() has the message.
 int llm_attention_decode(const void *q, long long q_stride, void *out, long long out_stride, const void *kc,
                          const void *vc, const int *tok_pos, const int *page_table, int pt_stride, int n_seqs,
-                         int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window, float scale,
+                         int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window, int block, float scale,
                          float *ws_o, float *ws_ml, cudaStream_t stream);
 
 // The same attention for callers that cannot allocate device memory and have no scratch to hand
@@ -44,7 +44,7 @@ int llm_attention_decode(const void *q, long long q_stride, void *out, long long
 long long llm_attention_decode_static_floats_needed(int n_seqs, int n_heads, int d, int n_splits);
 int llm_attention_decode_static(const void *q, long long q_stride, void *out, long long out_stride, const void *kc,
                                 const void *vc, const int *tok_pos, const int *page_table, int pt_stride, int n_seqs,
-                                int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window,
+                                int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window, int block,
                                 float scale, cudaStream_t stream);
 
 const char *llm_attention_decode_last_error(void);

@@ -20,7 +20,8 @@
 //    CTA that finishes last for a (sequence, kv head) joins the splits in split order, so the
 //    result does not depend on which one that is.
 // Head h reads kv head h / (heads / kv_heads); scores are scaled by `scale` (1/sqrt(d),
-// src/flint/operators.cc:43-56, 115-117); one query sees every cached key or the last `window`.
+// src/flint/operators.cc:43-56, 115-117); one query sees every cached key, the last `window`, or those
+// of its own block of `block` positions.
 #include "common.cuh"
 #include "mma_tiles.cuh"
 #include <math.h>
@@ -59,7 +60,7 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
                            int table_rows, int rot_dim, const int *__restrict__ tok_pos,
                            const int *__restrict__ page_table, int pt_stride, __nv_bfloat16 *__restrict__ kc,
                            __nv_bfloat16 *__restrict__ vc, int write_cache, int n_heads, int n_kv, int G, int chunk,
-                           int window, float scale_log2, float *__restrict__ ws_o, float *__restrict__ ws_ml,
+                           int window, int block, float scale_log2, float *__restrict__ ws_o, float *__restrict__ ws_ml,
                            int *__restrict__ counters, int n_splits, __nv_bfloat16 *__restrict__ out,
                            long long out_stride) {
   constexpr int LD = D + 8;
@@ -82,7 +83,7 @@ attention_decode_tc_kernel(const float *__restrict__ qkv, long long qkv_stride, 
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int pos = tok_pos[b];
   const int len = pos + 1;
-  const int kstart = window > 0 ? max(0, len - window) : 0;
+  const int kstart = max(window > 0 ? max(0, len - window) : 0, block > 0 ? (len - 1) / block * block : 0);
   // chunk 0: the sequence's own length cut into n_splits runs of whole pages, so that every split
   // has work whatever bound on the length the launch was shaped for
   if (chunk <= 0) chunk = max(DT_BN, ((len + n_splits - 1) / n_splits + DT_BN - 1) / DT_BN * DT_BN);
@@ -460,7 +461,7 @@ static int launch_decode_tc(const float *qkv, long long qkv_stride, int qkv_part
                             const float *table, int table_rows, int rot_dim,
                             const int *tok_pos, const int *page_table, int pt_stride, void *kc, void *vc,
                             int write_cache, int n_seqs, int n_heads, int n_kv, int chunk, int max_len, int n_splits,
-                            int window, float scale, float *ws_o, float *ws_ml, int *counters, void *out, long long out_stride,
+                            int window, int block, float scale, float *ws_o, float *ws_ml, int *counters, void *out, long long out_stride,
                             cudaStream_t stream) {
   constexpr int LD = D + 8;
   const size_t tiles = (size_t)(DT_ROWS + 2 + 2 * decode_tc_stages(D) * DT_BN) * LD * sizeof(__nv_bfloat16);
@@ -474,7 +475,7 @@ static int launch_decode_tc(const float *qkv, long long qkv_stride, int qkv_part
   LLM_CHECK_CUDA(llm_launch(kern, grid, dim3(DT_WARPS * 32), smem, stream, qkv, qkv_stride, qkv_parts, qkv_part_stride, table, table_rows,
                             rot_dim,
                             tok_pos, page_table, pt_stride, (__nv_bfloat16 *)kc, (__nv_bfloat16 *)vc, write_cache,
-                            n_heads, n_kv, n_heads / n_kv, chunk, window, scale * 1.4426950408889634f, ws_o, ws_ml,
+                            n_heads, n_kv, n_heads / n_kv, chunk, window, block, scale * 1.4426950408889634f, ws_o, ws_ml,
                             counters, n_splits, (__nv_bfloat16 *)out, out_stride),
                  "attention_decode_tc launch");
   return LLM_OK;
@@ -506,7 +507,7 @@ LLM_EXPORT int llm_attention_decode_tc(const float *qkv, long long qkv_stride, i
                                        long long qkv_part_stride, const float *table, int table_rows,
                                        int rot_dim, const int *tok_pos, const int *page_table, int pt_stride,
                                        void *kc, void *vc, int write_cache, int n_seqs, int n_heads, int n_kv, int d,
-                                       int page_size, int chunk, int max_len, int n_splits, int window, float scale,
+                                       int page_size, int chunk, int max_len, int n_splits, int window, int block, float scale,
                                        float *ws_o,
                                        float *ws_ml, int *counters, void *out, long long out_stride,
                                        cudaStream_t stream) {
@@ -527,7 +528,7 @@ LLM_EXPORT int llm_attention_decode_tc(const float *qkv, long long qkv_stride, i
 #define DT_CASE(DD)                                                                                                 \
   if (d == DD)                                                                                                      \
     return launch_decode_tc<DD>(qkv, qkv_stride, qkv_parts, qkv_part_stride, table, table_rows, rot_dim, tok_pos, page_table, pt_stride, kc, vc, \
-                                write_cache, n_seqs, n_heads, n_kv, chunk, max_len, n_splits, window, scale, ws_o,  \
+                                write_cache, n_seqs, n_heads, n_kv, chunk, max_len, n_splits, window, block, scale, ws_o,  \
                                 ws_ml,                                                                              \
                                 counters, out, out_stride, stream);
   DT_CASE(16) DT_CASE(32) DT_CASE(48) DT_CASE(64) DT_CASE(80) DT_CASE(96) DT_CASE(112) DT_CASE(128)

@@ -1,6 +1,8 @@
-// Causal grouped-query attention over the paged cache, any head size up to 256, any
-// number of heads and groups, optional sliding window; element type float or bfloat16,
-// arithmetic in 32-bit.  One warp serves one (token, head): lanes take 32 keys at a time
+// Causal grouped-query attention over the paged cache, any head size up to 256 (values may
+// have another width than keys), any number of heads and groups; optional sliding window,
+// optional block mask (a query sees only keys of its own block of `block` positions, blocks
+// counted from position 0), optional gate per (token, head) on the result (multiplied by
+// sigmoid(gate)); element type float or bfloat16, arithmetic in 32-bit.  One warp serves one (token, head): lanes take 32 keys at a time
 // for the scores, then 32 channels at a time for the weighted sum, with a running
 // maximum and sum (the online form of softmax, src/flint/cpu/softmax.cc:31-60).
 //
@@ -22,8 +24,12 @@ LLM_DEFINE_LAST_ERROR(llm_attention_generic_last_error)
 constexpr int WARPS = 4;
 constexpr int MAX_D = 256;
 
-__device__ __forceinline__ float dot_row(const float *q, const float *k, int d) {
+__device__ __forceinline__ float dot_row(const float *q, const float *k, int d, bool vec) {
   float acc = 0.f;
+  if (!vec) {
+    for (int c = 0; c < d; ++c) acc = fmaf(q[c], k[c], acc);
+    return acc;
+  }
   for (int c = 0; c < d; c += 4) {
     const float4 v = *reinterpret_cast<const float4 *>(k + c);
     acc = fmaf(q[c], v.x, acc);
@@ -33,8 +39,12 @@ __device__ __forceinline__ float dot_row(const float *q, const float *k, int d) 
   }
   return acc;
 }
-__device__ __forceinline__ float dot_row(const float *q, const __nv_bfloat16 *k, int d) {
+__device__ __forceinline__ float dot_row(const float *q, const __nv_bfloat16 *k, int d, bool vec) {
   float acc = 0.f;
+  if (!vec) {
+    for (int c = 0; c < d; ++c) acc = fmaf(q[c], __bfloat162float(k[c]), acc);
+    return acc;
+  }
   for (int c = 0; c < d; c += 8) {
     const uint4 raw = *reinterpret_cast<const uint4 *>(k + c);
     const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
@@ -54,8 +64,9 @@ attention_generic_kernel(const T *__restrict__ q, long long q_stride, T *__restr
                          long long out_stride, const T *__restrict__ kcache,
                          const T *__restrict__ vcache, const int *__restrict__ tok_seq,
                          const int *__restrict__ tok_pos, const int *__restrict__ page_table,
-                         int pt_stride, int n_tokens, int n_heads, int n_kv, int d, int page_size,
-                         int window, float scale) {
+                         int pt_stride, int n_tokens, int n_heads, int n_kv, int d, int dv, int page_size,
+                         int window, int block, float scale, const float *__restrict__ gate,
+                         long long gate_stride, int vec) {
   __shared__ __align__(16) float q_s[WARPS][MAX_D];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long w = (long long)blockIdx.x * WARPS + warp;
@@ -68,7 +79,8 @@ attention_generic_kernel(const T *__restrict__ q, long long q_stride, T *__restr
   for (int c = lane; c < d; c += 32) q_s[warp][c] = to_float(qrow[c]);
   __syncwarp();
 
-  const int kstart = window > 0 ? max(0, p - window + 1) : 0;
+  int kstart = window > 0 ? max(0, p - window + 1) : 0;
+  if (block > 0) kstart = max(kstart, p / block * block);
   float m = -INFINITY, l = 0.f;
   float acc[MAX_D / 32];
 #pragma unroll
@@ -81,7 +93,7 @@ attention_generic_kernel(const T *__restrict__ q, long long q_stride, T *__restr
     if (valid) {
       const int page = pt[j / page_size];
       const T *krow = kcache + (((size_t)page * n_kv + kvh) * page_size + (j % page_size)) * d;
-      s = dot_row(q_s[warp], krow, d) * scale;
+      s = dot_row(q_s[warp], krow, d, vec != 0) * scale;
     }
     const float m_new = fmaxf(m, warp_max(s));          // finite: lane 0 always holds a key
     const float pj = valid ? expf(s - m_new) : 0.f;
@@ -94,46 +106,50 @@ attention_generic_kernel(const T *__restrict__ q, long long q_stride, T *__restr
       const float pv = __shfl_sync(0xffffffffu, pj, jj);
       const int key = kb + jj;
       const int page = pt[key / page_size];
-      const T *vrow = vcache + (((size_t)page * n_kv + kvh) * page_size + (key % page_size)) * d;
+      const T *vrow = vcache + (((size_t)page * n_kv + kvh) * page_size + (key % page_size)) * dv;
 #pragma unroll
       for (int i = 0; i < MAX_D / 32; ++i) {
         const int c = lane + 32 * i;
-        if (c < d) acc[i] = fmaf(pv, to_float(vrow[c]), acc[i]);
+        if (c < dv) acc[i] = fmaf(pv, to_float(vrow[c]), acc[i]);
       }
     }
     m = m_new;
   }
-  T *orow = out + (size_t)token * out_stride + (size_t)h * d;
-  const float inv = 1.f / l;
+  T *orow = out + (size_t)token * out_stride + (size_t)h * dv;
+  float inv = 1.f / l;
+  if (gate) inv *= 1.f / (1.f + expf(-gate[(size_t)token * gate_stride + h]));
 #pragma unroll
   for (int i = 0; i < MAX_D / 32; ++i) {
     const int c = lane + 32 * i;
-    if (c < d) orow[c] = from_float<T>(acc[i] * inv);
+    if (c < dv) orow[c] = from_float<T>(acc[i] * inv);
   }
 }
 
 LLM_EXPORT int llm_attention_generic(int dtype, const void *q, long long q_stride, void *out,
                                      long long out_stride, const void *kcache, const void *vcache,
                                      const int *tok_seq, const int *tok_pos, const int *page_table,
-                                     int pt_stride, int n_tokens, int n_heads, int n_kv, int d,
-                                     int page_size, int window, float scale, cudaStream_t stream) {
+                                     int pt_stride, int n_tokens, int n_heads, int n_kv, int d, int dv,
+                                     int page_size, int window, int block, float scale, const float *gate,
+                                     long long gate_stride, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0, "attention: bad head counts %d/%d", n_heads, n_kv);
-  LLM_REQUIRE(d > 0 && d <= MAX_D && d % 8 == 0, "attention: head size %d is not supported (a multiple of 8 up to %d)", d, MAX_D);
-  LLM_REQUIRE(q_stride % 4 == 0, "attention: q rows must be 16-byte aligned");
+  LLM_REQUIRE(d > 0 && d <= MAX_D && dv > 0 && dv <= MAX_D, "attention: head sizes %d / %d are not supported (up to %d)", d, dv, MAX_D);
+  LLM_REQUIRE(window >= 0 && block >= 0, "attention: bad window or block");
+  // 16-byte loads of key rows where rows start on such a boundary
+  const int vec = (dtype == LLM_F32 ? d % 4 == 0 : d % 8 == 0) && (uintptr_t)kcache % 16 == 0;
   const long long warps = (long long)n_tokens * n_heads;
   const long long blocks = (warps + WARPS - 1) / WARPS;
   LLM_REQUIRE(blocks < 2147483647LL, "attention: too many tokens for one launch");
   if (dtype == LLM_F32) {
-    LLM_REQUIRE(d % 4 == 0, "attention: head size");
     attention_generic_kernel<float><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
         (const float *)q, q_stride, (float *)out, out_stride, (const float *)kcache, (const float *)vcache,
-        tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, n_kv, d, page_size, window, scale);
+        tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, n_kv, d, dv, page_size, window, block, scale,
+        gate, gate_stride, vec);
   } else if (dtype == LLM_BF16) {
     attention_generic_kernel<__nv_bfloat16><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
         (const __nv_bfloat16 *)q, q_stride, (__nv_bfloat16 *)out, out_stride, (const __nv_bfloat16 *)kcache,
-        (const __nv_bfloat16 *)vcache, tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, n_kv, d,
-        page_size, window, scale);
+        (const __nv_bfloat16 *)vcache, tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, n_kv, d, dv,
+        page_size, window, block, scale, gate, gate_stride, vec);
   } else {
     LLM_FAIL("attention: unknown dtype %d", dtype);
   }

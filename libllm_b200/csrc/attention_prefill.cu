@@ -37,7 +37,7 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
                          long long out_stride, const __nv_bfloat16 *__restrict__ kc,
                          const __nv_bfloat16 *__restrict__ vc, const int *__restrict__ seq_start,
                          const int *__restrict__ seq_past, const int *__restrict__ page_table, int pt_stride,
-                         int n_heads, int n_kv, int window, float scale_log2) {
+                         int n_heads, int n_kv, int window, int block, float scale_log2) {
   constexpr int LD = D + 8;                                  // padded row, in elements
   constexpr int CHUNKS = D / 8;                              // 16-byte pieces of a row
   constexpr int KS = D / 16;                                 // k-steps of Q K^T
@@ -62,7 +62,11 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
 
   // key tiles this CTA needs: the first row's window start .. the last row's own position
   const int last_tile = (past + r0 + rows - 1) / AP_BN;
-  const int first_tile = window > 0 ? max(0, past + r0 - window + 1) / AP_BN : 0;
+  int first_key = window > 0 ? max(0, past + r0 - window + 1) : 0;
+  if (block > 0) first_key = max(first_key, (past + r0) / block * block);      // the first row's block starts here
+  const int first_tile = first_key / AP_BN;
+  // keys before this one are hidden from the CTA's last row by the block mask (0: no such mask)
+  const int block_edge = block > 0 ? (past + r0 + rows - 1) / block * block : 0;
   const int *pt = page_table + (size_t)b * pt_stride;
 
   auto load_kv = [&](int kt, int stage) {
@@ -126,7 +130,7 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
 
     // mask: key j is seen by the row at position p when j <= p and (no window or j > p - window)
     const int k0 = kt * AP_BN;
-    const bool edge = (k0 + AP_BN - 1 > past + r0) || (window > 0 && k0 <= past + r0 + AP_BM - 1 - window);
+    const bool edge = (k0 + AP_BN - 1 > past + r0) || (window > 0 && k0 <= past + r0 + AP_BM - 1 - window) || k0 < block_edge;
     if (edge) {
 #pragma unroll
       for (int n = 0; n < NT; ++n)
@@ -134,7 +138,7 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
         for (int j = 0; j < 4; ++j) {
           const int key = k0 + n * 8 + 2 * t + (j & 1);
           const int p = (j & 2) ? pos1 : pos0;
-          const bool seen = key <= p && (window <= 0 || key > p - window);
+          const bool seen = key <= p && (window <= 0 || key > p - window) && (block <= 0 || key >= p / block * block);
           if (!seen) s[n][j] = -INFINITY;
         }
     }
@@ -217,7 +221,7 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
 template <int D>
 static int launch_prefill(const void *q, long long q_stride, void *out, long long out_stride, const void *kc,
                           const void *vc, const int *seq_start, const int *seq_past, const int *page_table,
-                          int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int window, float scale,
+                          int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int window, int block, float scale,
                           cudaStream_t stream) {
   constexpr int LD = D + 8;
   const size_t smem = (size_t)(AP_BM + 4 * AP_BN) * LD * sizeof(__nv_bfloat16);
@@ -226,7 +230,7 @@ static int launch_prefill(const void *q, long long q_stride, void *out, long lon
   dim3 grid((max_q_len + AP_BM - 1) / AP_BM, n_heads, n_seqs);
   llm_launch(kern, grid, dim3(AP_WARPS * 32), smem, stream, (const __nv_bfloat16 *)q, q_stride, (__nv_bfloat16 *)out,
              out_stride, (const __nv_bfloat16 *)kc, (const __nv_bfloat16 *)vc, seq_start, seq_past, page_table,
-             pt_stride, n_heads, n_kv, window, scale * 1.4426950408889634f);
+             pt_stride, n_heads, n_kv, window, block, scale * 1.4426950408889634f);
   LLM_CHECK_LAUNCH("attention_prefill");
   return LLM_OK;
 }
@@ -242,7 +246,7 @@ LLM_EXPORT int llm_attention_prefill_supports(int d, int page_size) {
 LLM_EXPORT int llm_attention_prefill(const void *q, long long q_stride, void *out, long long out_stride,
                                      const void *kc, const void *vc, const int *seq_start, const int *seq_past,
                                      const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads,
-                                     int n_kv, int d, int page_size, int window, float scale, cudaStream_t stream) {
+                                     int n_kv, int d, int page_size, int window, int block, float scale, cudaStream_t stream) {
   if (n_seqs == 0 || max_q_len == 0) return LLM_OK;
   LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_heads > 0 && n_heads <= 65535 && n_kv > 0 && n_heads % n_kv == 0,
               "attention_prefill: bad sizes (%d sequences, %d heads, %d kv heads)", n_seqs, n_heads, n_kv);
@@ -252,10 +256,11 @@ LLM_EXPORT int llm_attention_prefill(const void *q, long long q_stride, void *ou
   LLM_REQUIRE(q_stride % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)kc % 16 == 0 && (uintptr_t)vc % 16 == 0,
               "attention_prefill: rows must be 16-byte aligned");
   LLM_REQUIRE(out_stride % 2 == 0 && (uintptr_t)out % 4 == 0, "attention_prefill: output rows must be 4-byte aligned");
+  LLM_REQUIRE(window >= 0 && block >= 0 && scale > 0.f, "attention_prefill: bad window, block or scale");
 #define AP_CASE(DD)                                                                                                  \
   if (d == DD)                                                                                                       \
     return launch_prefill<DD>(q, q_stride, out, out_stride, kc, vc, seq_start, seq_past, page_table, pt_stride,      \
-                              n_seqs, max_q_len, n_heads, n_kv, window, scale, stream);
+                              n_seqs, max_q_len, n_heads, n_kv, window, block, scale, stream);
   AP_CASE(16) AP_CASE(32) AP_CASE(48) AP_CASE(64) AP_CASE(80) AP_CASE(96) AP_CASE(112) AP_CASE(128)
 #undef AP_CASE
   LLM_FAIL("attention_prefill: no kernel for head size %d", d);

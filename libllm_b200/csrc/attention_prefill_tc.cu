@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(FT_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16 *__restrict__ out,
                             long long out_stride, const int *__restrict__ seq_start, const int *__restrict__ seq_past,
-                            const int *__restrict__ page_table, int pt_stride, int n_heads, int n_kv, int window,
+                            const int *__restrict__ page_table, int pt_stride, int n_heads, int n_kv, int window, int block,
                             float scale_log2, int *status) {
   using S = FtShape<D>;
   constexpr int STAGES = S::STAGES;
@@ -152,7 +152,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int rows = active ? min(FT_BM, n_q - r0) : 0;
   const int kvh = h / (n_heads / n_kv);
   const int last_tile = active ? (past + r0 + rows - 1) / FT_BN : -1;
-  const int first_tile = window > 0 ? max(0, past + r0 - window + 1) / FT_BN : 0;
+  // the first key the CTA's first row sees; keys before block_edge are hidden from its last row by the block mask
+  const int first_tile = max(window > 0 ? max(0, past + r0 - window + 1) : 0, block > 0 ? (past + r0) / block * block : 0) / FT_BN;
+  const int block_edge = block > 0 && active ? (past + r0 + rows - 1) / block * block : 0;
   const int n_tiles = last_tile - first_tile + 1;             // <= 0: nothing to do
   const int *pt = page_table + (size_t)b * pt_stride;
 
@@ -285,13 +287,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tc_ld_wait();
         tc_ld_ready(own[0]);
         tc_ld_ready(own[1]);
-        if ((k0 + 31 > past + r0) || (window > 0 && k0 <= past + r0 + FT_BM - 1 - window)) {
+        if ((k0 + 31 > past + r0) || (window > 0 && k0 <= past + r0 + FT_BM - 1 - window) || k0 < block_edge) {
+          const int vis_lo = max(window > 0 ? pos - window + 1 : 0, block > 0 ? pos / block * block : 0);
 #pragma unroll
           for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const int key = k0 + c * 16 + i;
-              if (!(key <= pos && (window <= 0 || key > pos - window))) own[c][i] = -INFINITY;
+              if (!(key <= pos && key >= vis_lo)) own[c][i] = -INFINITY;
             }
         }
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of sixteen
@@ -456,7 +459,7 @@ __global__ void __launch_bounds__(FW_THREADS, 1)
 attention_prefill_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                               const __grid_constant__ CUtensorMap map_v, __nv_bfloat16 *__restrict__ out,
                               long long out_stride, const int *__restrict__ seq_start, const int *__restrict__ seq_past,
-                              const int *__restrict__ page_table, int pt_stride, int n_heads, int n_kv, int window,
+                              const int *__restrict__ page_table, int pt_stride, int n_heads, int n_kv, int window, int block,
                               float scale_log2, int *status) {
   using S = FwShape<D>;
   constexpr int STAGES = S::STAGES;
@@ -519,10 +522,12 @@ attention_prefill_wide_kernel(const __grid_constant__ CUtensorMap map_q, const _
   const int kvh = h / (n_heads / n_kv);
   // Key tiles of the two query tiles: A works on tiles [0, n_a) of the CTA's range, B on [j_b0, n_tiles).
   const bool has_b = rows > 128;
-  const int first_tile = window > 0 ? max(0, past + r0 - window + 1) / FW_BN : 0;
+  const int first_tile = max(window > 0 ? max(0, past + r0 - window + 1) : 0, block > 0 ? (past + r0) / block * block : 0) / FW_BN;
   const int n_a = active ? (past + r0 + min(rows, 128) - 1) / FW_BN - first_tile + 1 : 0;
   const int n_tiles = has_b ? (past + r0 + rows - 1) / FW_BN - first_tile + 1 : n_a;
-  const int j_b0 = has_b ? (window > 0 ? max(0, past + r0 + 128 - window + 1) / FW_BN : 0) - first_tile : n_tiles;
+  const int j_b0 = has_b ? max(window > 0 ? max(0, past + r0 + 128 - window + 1) : 0,
+                               block > 0 ? (past + r0 + 128) / block * block : 0) / FW_BN - first_tile
+                         : n_tiles;
   const int *pt = page_table + (size_t)b * pt_stride;
 
   if (warp >= 8) {
@@ -686,13 +691,14 @@ attention_prefill_wide_kernel(const __grid_constant__ CUtensorMap map_q, const _
         if (lane == 0) mbar_arrive(bar_sfree + 8 * x);
       }
       const int k0 = (first_tile + j) * FW_BN;
-      if (k0 + FW_BN - 1 > pos_lo || (window > 0 && k0 <= pos_lo + 31 - window)) {
+      if (k0 + FW_BN - 1 > pos_lo || (window > 0 && k0 <= pos_lo + 31 - window) || (block > 0 && k0 < (pos_lo + 31) / block * block)) {
+        const int vis_lo = max(window > 0 ? pos - window + 1 : 0, block > 0 ? pos / block * block : 0);
 #pragma unroll
         for (int g = 0; g < 8; ++g)
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int key = k0 + g * 16 + i;
-            if (!(key <= pos && (window <= 0 || key > pos - window))) sc[g][i] = -INFINITY;
+            if (!(key <= pos && key >= vis_lo)) sc[g][i] = -INFINITY;
           }
       }
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -816,7 +822,7 @@ template <int D>
 int launch_prefill_tc(const void *q, long long q_stride, long long n_tokens, void *out, long long out_stride,
                       const void *kc, const void *vc, long long n_pages, const int *seq_start, const int *seq_past,
                       const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int window,
-                      float scale, int form, int *status, cudaStream_t stream) {
+                      int block, float scale, int form, int *status, cudaStream_t stream) {
   using S = FtShape<D>;
   CUtensorMap map_q, map_k, map_v;
   int rc = get_map(q, n_tokens, (long long)n_heads * D, q_stride, 64, &map_q);
@@ -835,7 +841,7 @@ int launch_prefill_tc(const void *q, long long q_stride, long long n_tokens, voi
     LLM_CHECK_CUDA(llm_allow_smem(kern, W::SMEM), "attention_prefill_tc attribute");
     dim3 grid(n_heads, n_seqs, (max_q_len + FW_BM - 1) / FW_BM);
     LLM_CHECK_CUDA(llm_launch(kern, grid, dim3(FW_THREADS), W::SMEM, stream, map_q, map_k, map_v, (__nv_bfloat16 *)out,
-                              out_stride, seq_start, seq_past, page_table, pt_stride, n_heads, n_kv, window,
+                              out_stride, seq_start, seq_past, page_table, pt_stride, n_heads, n_kv, window, block,
                               scale * 1.4426950408889634f, status),
                    "attention_prefill_tc launch");
     return LLM_OK;
@@ -844,7 +850,7 @@ int launch_prefill_tc(const void *q, long long q_stride, long long n_tokens, voi
   LLM_CHECK_CUDA(llm_allow_smem(kern, S::SMEM), "attention_prefill_tc attribute");
   dim3 grid(n_heads, n_seqs, (max_q_len + FT_BM - 1) / FT_BM);
   LLM_CHECK_CUDA(llm_launch(kern, grid, dim3(FT_THREADS), S::SMEM, stream, map_q, map_k, map_v, (__nv_bfloat16 *)out,
-                            out_stride, seq_start, seq_past, page_table, pt_stride, n_heads, n_kv, window,
+                            out_stride, seq_start, seq_past, page_table, pt_stride, n_heads, n_kv, window, block,
                             scale * 1.4426950408889634f, status),
                  "attention_prefill_tc launch");
   return LLM_OK;
@@ -866,7 +872,7 @@ LLM_EXPORT int llm_attention_prefill_tc(const void *q, long long q_stride, long 
                                         long long out_stride, const void *kc, const void *vc, long long n_pages,
                                         const int *seq_start, const int *seq_past, const int *page_table,
                                         int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int d,
-                                        int page_size, int window, float scale, int form, int *status,
+                                        int page_size, int window, int block, float scale, int form, int *status,
                                         cudaStream_t stream) {
   if (n_seqs == 0 || max_q_len == 0) return LLM_OK;
   LLM_REQUIRE(form >= 0 && form <= 2, "attention_prefill_tc: form %d is not one of 0, 1, 2", form);
@@ -878,10 +884,11 @@ LLM_EXPORT int llm_attention_prefill_tc(const void *q, long long q_stride, long 
   LLM_REQUIRE(q_stride % 8 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)kc % 16 == 0 && (uintptr_t)vc % 16 == 0 &&
                   out_stride % 8 == 0 && (uintptr_t)out % 16 == 0,
               "attention_prefill_tc: rows must be 16-byte aligned");
+  LLM_REQUIRE(window >= 0 && block >= 0 && scale > 0.f, "attention_prefill_tc: bad window, block or scale");
   LLM_REQUIRE(n_pages * n_kv * FT_BN < (1ll << 31), "attention_prefill_tc: the cache has too many rows for one tensor map");
   if (d == 64)
     return launch_prefill_tc<64>(q, q_stride, n_tokens, out, out_stride, kc, vc, n_pages, seq_start, seq_past, page_table,
-                                 pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, scale, form, status, stream);
+                                 pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, block, scale, form, status, stream);
   return launch_prefill_tc<128>(q, q_stride, n_tokens, out, out_stride, kc, vc, n_pages, seq_start, seq_past, page_table,
-                                pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, scale, form, status, stream);
+                                pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, block, scale, form, status, stream);
 }

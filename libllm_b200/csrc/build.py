@@ -50,6 +50,7 @@ FAMILIES: Dict[str, dict] = {
     "rope": dict(sources=["rope.cu"], headers=["common.cuh"]),
     "attention_generic": dict(sources=["attention_generic.cu"], headers=["common.cuh"]),
     "sampling": dict(sources=["sampling.cu"], headers=["common.cuh"]),
+    "moe": dict(sources=["moe.cu"], headers=["common.cuh", "mma_tiles.cuh"]),
     "gemv": dict(sources=["gemv.cu"], headers=["common.cuh"]),
     "attention_decode": dict(sources=["attention_decode.cu"], headers=["common.cuh", "attention_decode.h"]),
     "attention_prefill": dict(sources=["attention_prefill.cu"], headers=["common.cuh", "mma_tiles.cuh"]),

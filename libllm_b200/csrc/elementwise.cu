@@ -430,3 +430,78 @@ LLM_EXPORT int llm_random_fill(void *out, int dtype, long long n, unsigned long 
   LLM_CHECK_LAUNCH("random_fill");
   return LLM_OK;
 }
+
+// ---------------------------------------------------------------- the stream beside another tensor
+// out[t] = [resid[t] + sum_p delta[p][t] | other[t]], two rows of `hidden` values side by side in
+// the type of out: the input of a projection that mixes the residual stream with a second tensor
+// of the same shape (the token rows, for a model that feeds them to every pass of a loop).
+template <typename TO>
+__global__ void concat_stream_kernel(const float *__restrict__ resid, const float *__restrict__ delta, int n_parts,
+                                     size_t part_stride, const float *__restrict__ other, TO *__restrict__ out,
+                                     int hidden, size_t total) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / hidden;
+    const int c = (int)(idx - t * hidden);
+    float v = resid[idx];
+    for (int p = 0; p < n_parts; ++p) v += delta[p * part_stride + idx];
+    out[t * 2 * hidden + c] = from_float<TO>(v);
+    out[t * 2 * hidden + hidden + c] = from_float<TO>(other[idx]);
+  }
+}
+
+LLM_EXPORT int llm_concat_stream(const float *resid, const float *delta, int n_parts, long long part_stride,
+                                 const float *other, void *out, int out_dtype, int n_rows, int hidden,
+                                 cudaStream_t stream) {
+  if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && hidden > 0 && resid && other && out && n_parts >= 0, "concat_stream: bad arguments");
+  if (!delta) n_parts = 0;
+  const size_t total = (size_t)n_rows * hidden;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > (size_t)sm_count() * 32) blocks = (size_t)sm_count() * 32;
+  if (out_dtype == LLM_F32)
+    llm_launch(concat_stream_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, resid, delta, n_parts,
+               (size_t)part_stride, other, (float *)out, hidden, total);
+  else if (out_dtype == LLM_BF16)
+    llm_launch(concat_stream_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, resid, delta, n_parts,
+               (size_t)part_stride, other, (__nv_bfloat16 *)out, hidden, total);
+  else LLM_FAIL("concat_stream: unknown dtype %d", out_dtype);
+  LLM_CHECK_LAUNCH("concat_stream");
+  return LLM_OK;
+}
+
+// ---------------------------------------------------------------- a gate per head
+// x[t, h * dv + c] *= sigmoid(gate[t * gate_stride + h]): the output gate of an attention whose
+// kernel does not apply it itself.  The gate is 32-bit (a column block of the stacked product).
+template <typename T>
+__global__ void head_gate_kernel(T *__restrict__ x, long long ld, const float *__restrict__ gate, long long gate_stride,
+                                 int n_heads, int dv, size_t total) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  const int width = n_heads * dv;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / width;
+    const int c = (int)(idx - t * width);
+    const float g = 1.f / (1.f + expf(-gate[t * gate_stride + c / dv]));
+    T *p = x + t * ld + c;
+    *p = from_float<T>(to_float(*p) * g);
+  }
+}
+
+LLM_EXPORT int llm_head_gate(void *x, int dtype, long long ld, const float *gate, long long gate_stride, int n_tokens,
+                             int n_heads, int dv, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && dv > 0 && x && gate, "head_gate: bad arguments");
+  const size_t total = (size_t)n_tokens * n_heads * dv;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > (size_t)sm_count() * 32) blocks = (size_t)sm_count() * 32;
+  if (dtype == LLM_F32)
+    llm_launch(head_gate_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, (float *)x, ld, gate, gate_stride, n_heads, dv, total);
+  else if (dtype == LLM_BF16)
+    llm_launch(head_gate_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, (__nv_bfloat16 *)x, ld, gate,
+               gate_stride, n_heads, dv, total);
+  else LLM_FAIL("head_gate: unknown dtype %d", dtype);
+  LLM_CHECK_LAUNCH("head_gate");
+  return LLM_OK;
+}

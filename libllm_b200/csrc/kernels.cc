@@ -168,6 +168,14 @@ void gather_rows_add(const float *resid, const Act *delta, const int *rows, int 
   LLM_CALL("elementwise", llm_gather_rows_add, resid, has ? delta->data : nullptr, has ? code(delta->dtype) : 0, has ? delta->parts : 0,
            has ? (long long)delta->part_stride : 0, rows, n_rows, out, hidden, s);
 }
+LLM_KERNEL("elementwise", llm_concat_stream, const float *, const float *, int, long long, const float *, void *, int, int, int,
+           cudaStream_t)
+void concat_stream(const float *resid, const Act *delta, const float *other, const Act &out, int hidden, cudaStream_t s) {
+  const bool has = delta && delta->data;
+  if (has && delta->dtype != DType::F32) LLM_THROW(InvalidArg, "concat_stream: a pending addition is 32-bit");
+  LLM_CALL("elementwise", llm_concat_stream, resid, has ? (const float *)delta->data : nullptr, has ? delta->parts : 0,
+           has ? (long long)delta->part_stride : 0, other, out.data, code(out.dtype), (int)out.rows, hidden, s);
+}
 void swiglu(const Act &gu, void *out, DType out_dtype, cudaStream_t s) {
   LLM_CALL("elementwise", llm_swiglu, code(gu.dtype), code(out_dtype), gu.data, out, (int)gu.rows, (int)(gu.cols / 2), s);
 }
@@ -255,25 +263,42 @@ void rope_cache_write(const Act &qkv, const Act &q_out, int n_heads, int n_kv, i
            pt_stride, kcache, vcache, page_size, write_cache ? 1 : 0, s);
 }
 
+LLM_KERNEL("rope", llm_qk_place, int, int, const void *, long long, void *, long long, int, int, int, int, int, const float *,
+           const float *, float, const float *, int, int, const int *, const int *, const int *, int, void *, void *, int, int,
+           cudaStream_t)
+void qk_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, int dv, const float *q_norm, const float *k_norm,
+              float eps, const float *table, int table_rows, int rot_dim, const int *tok_seq, const int *tok_pos,
+              const int *page_table, int pt_stride, void *kcache, void *vcache, int page_size, bool write_cache, cudaStream_t s) {
+  LLM_CALL("rope", llm_qk_place, code(qkv.dtype), code(q_out.dtype), qkv.data, (long long)qkv.ld, q_out.data, (long long)q_out.ld,
+           (int)qkv.rows, n_heads, n_kv, d, dv, q_norm, k_norm, eps, table, table_rows, rot_dim, tok_seq, tok_pos, page_table,
+           pt_stride, kcache, vcache, page_size, write_cache ? 1 : 0, s);
+}
+
 // ---------------------------------------------------------------- attention
 LLM_KERNEL("attention_generic", llm_attention_generic, int, const void *, long long, void *, long long, const void *, const void *,
-           const int *, const int *, const int *, int, int, int, int, int, int, int, float, cudaStream_t)
+           const int *, const int *, const int *, int, int, int, int, int, int, int, int, int, float, const float *, long long,
+           cudaStream_t)
 LLM_KERNEL("attention_decode", llm_attention_decode, const void *, long long, void *, long long, const void *, const void *,
-           const int *, const int *, int, int, int, int, int, int, int, int, int, float, float *, float *, cudaStream_t)
+           const int *, const int *, int, int, int, int, int, int, int, int, int, int, float, float *, float *, cudaStream_t)
 LLM_KERNEL("attention_decode_tc", llm_attention_decode_tc, const float *, long long, int, long long, const float *, int, int,
-           const int *, const int *, int, void *, void *, int, int, int, int, int, int, int, int, int, int, float, float *,
+           const int *, const int *, int, void *, void *, int, int, int, int, int, int, int, int, int, int, int, float, float *,
            float *, int *, void *, long long, cudaStream_t)
 LLM_KERNEL("attention_prefill", llm_attention_prefill, const void *, long long, void *, long long, const void *, const void *,
-           const int *, const int *, const int *, int, int, int, int, int, int, int, int, float, cudaStream_t)
+           const int *, const int *, const int *, int, int, int, int, int, int, int, int, int, float, cudaStream_t)
+LLM_KERNEL("elementwise", llm_head_gate, void *, int, long long, const float *, long long, int, int, int, cudaStream_t)
+void head_gate(const Act &out, const float *gate, long long gate_stride, int n_heads, int dv, cudaStream_t s) {
+  LLM_CALL("elementwise", llm_head_gate, out.data, code(out.dtype), (long long)out.ld, gate, gate_stride, (int)out.rows, n_heads, dv, s);
+}
 LLM_KERNEL("attention_prefill_tc", llm_attention_prefill_tc, const void *, long long, long long, void *, long long, const void *,
-           const void *, long long, const int *, const int *, const int *, int, int, int, int, int, int, int, int, float, int,
+           const void *, long long, const int *, const int *, const int *, int, int, int, int, int, int, int, int, int, float, int,
            int *, cudaStream_t)
 
 void attention_generic(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_seq, const int *tok_pos,
-                       const int *page_table, int pt_stride, int n_heads, int n_kv, int d, int page_size, int window,
-                       float scale, cudaStream_t s) {
+                       const int *page_table, int pt_stride, int n_heads, int n_kv, int d, int dv, int page_size, int window,
+                       int block, float scale, const float *gate, long long gate_stride, cudaStream_t s) {
   LLM_CALL("attention_generic", llm_attention_generic, code(q.dtype), q.data, (long long)q.ld, out.data, (long long)out.ld, kc, vc,
-           tok_seq, tok_pos, page_table, pt_stride, (int)q.rows, n_heads, n_kv, d, page_size, window, scale, s);
+           tok_seq, tok_pos, page_table, pt_stride, (int)q.rows, n_heads, n_kv, d, dv, page_size, window, block, scale, gate,
+           gate_stride, s);
 }
 bool attention_decode_supported(int d, int group) {
   static auto f = resolve<int (*)(int, int)>("attention_decode", "llm_attention_decode_supports");
@@ -281,11 +306,11 @@ bool attention_decode_supported(int d, int group) {
 }
 void attention_decode(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                       int pt_stride, int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window,
-                      float scale, float *ws_o, float *ws_ml, cudaStream_t s) {
+                      int block, float scale, float *ws_o, float *ws_ml, cudaStream_t s) {
   const int B = (int)q.rows;
   LLM_CALL("attention_decode", llm_attention_decode, q.data, (long long)(B > 1 ? q.ld : q.cols), out.data,
            (long long)(B > 1 ? out.ld : out.cols), kc, vc, tok_pos, page_table, pt_stride, B, n_heads, n_kv, d, page_size, chunk,
-           n_splits, window, scale, ws_o, ws_ml, s);
+           n_splits, window, block, scale, ws_o, ws_ml, s);
 }
 bool attention_decode_tc_supported(int d, int page_size, int group) {
   static auto f = resolve<int (*)(int, int, int)>("attention_decode_tc", "llm_attention_decode_tc_supports");
@@ -297,11 +322,11 @@ int attention_decode_tc_ctas_per_sm(int d) {
 }
 void attention_decode_tc(const Act &qkv, const float *table, int table_rows, int rot_dim, const int *tok_pos,
                          const int *page_table, int pt_stride, void *kc, void *vc, bool write_cache, int n_seqs, int n_heads,
-                         int n_kv, int d, int page_size, int chunk, int max_len, int n_splits, int window, float scale,
-                         float *ws_o, float *ws_ml, int *counters, const Act &out, cudaStream_t s) {
+                         int n_kv, int d, int page_size, int chunk, int max_len, int n_splits, int window, int block,
+                         float scale, float *ws_o, float *ws_ml, int *counters, const Act &out, cudaStream_t s) {
   LLM_CALL("attention_decode_tc", llm_attention_decode_tc, (const float *)qkv.data, (long long)(n_seqs > 1 ? qkv.ld : qkv.cols),
            qkv.parts, (long long)qkv.part_stride, table, table_rows, rot_dim, tok_pos, page_table, pt_stride, kc, vc,
-           write_cache ? 1 : 0, n_seqs, n_heads, n_kv, d, page_size, chunk, max_len, n_splits, window, scale, ws_o, ws_ml,
+           write_cache ? 1 : 0, n_seqs, n_heads, n_kv, d, page_size, chunk, max_len, n_splits, window, block, scale, ws_o, ws_ml,
            counters, out.data, (long long)(n_seqs > 1 ? out.ld : out.cols), s);
 }
 bool attention_prefill_supported(int d, int page_size) {
@@ -310,9 +335,9 @@ bool attention_prefill_supported(int d, int page_size) {
 }
 void attention_prefill(const Act &q, const Act &out, const void *kc, const void *vc, const int *seq_start, const int *seq_past,
                        const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int d,
-                       int page_size, int window, float scale, cudaStream_t s) {
+                       int page_size, int window, int block, float scale, cudaStream_t s) {
   LLM_CALL("attention_prefill", llm_attention_prefill, q.data, (long long)q.ld, out.data, (long long)out.ld, kc, vc, seq_start,
-           seq_past, page_table, pt_stride, n_seqs, max_q_len, n_heads, n_kv, d, page_size, window, scale, s);
+           seq_past, page_table, pt_stride, n_seqs, max_q_len, n_heads, n_kv, d, page_size, window, block, scale, s);
 }
 bool attention_prefill_tc_supported(int d, int page_size) {
   static auto f = resolve<int (*)(int, int)>("attention_prefill_tc", "llm_attention_prefill_tc_supports");
@@ -320,10 +345,49 @@ bool attention_prefill_tc_supported(int d, int page_size) {
 }
 void attention_prefill_tc(const Act &q, const Act &out, const void *kc, const void *vc, long long n_pages, const int *seq_start,
                           const int *seq_past, const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads,
-                          int n_kv, int d, int page_size, int window, float scale, int *status, cudaStream_t s) {
+                          int n_kv, int d, int page_size, int window, int block, float scale, int *status, cudaStream_t s) {
   LLM_CALL("attention_prefill_tc", llm_attention_prefill_tc, q.data, (long long)q.ld, (long long)q.rows, out.data,
            (long long)out.ld, kc, vc, n_pages, seq_start, seq_past, page_table, pt_stride, n_seqs, max_q_len, n_heads, n_kv, d,
-           page_size, window, scale, 0, status, s);
+           page_size, window, block, scale, 0, status, s);
+}
+
+// ---------------------------------------------------------------- routed feed-forward
+LLM_KERNEL("moe", llm_activation, int, int, const void *, void *, long long, int, cudaStream_t)
+LLM_KERNEL("moe", llm_moe_route, const float *, long long, int, int, int, int, int, int *, float *, cudaStream_t)
+LLM_KERNEL("moe", llm_moe_sort, const int *, int, int, int, int *, int *, int *, cudaStream_t)
+LLM_KERNEL("moe", llm_moe_rows, int, const void *, long long, const void *, const void *, const int *, const float *, int, int, int,
+           int, int, int, float *, cudaStream_t)
+LLM_KERNEL("moe", llm_moe_grouped, const void *, long long, const void *, const void *, const int *, const int *, const int *,
+           const float *, int, int, int, int, int, int, int, void *, float *, cudaStream_t)
+void activation(const Act &in, const Act &out, int act, cudaStream_t s) {
+  if (in.ld != in.cols || out.ld != out.cols) LLM_THROW(InvalidArg, "activation: rows must be dense");
+  LLM_CALL("moe", llm_activation, code(in.dtype), code(out.dtype), in.data, out.data, (long long)(in.rows * in.cols), act, s);
+}
+void moe_route(const Act &logits, int n_experts, int top, int score, bool renormalize, int *chosen, float *weight, cudaStream_t s) {
+  LLM_CALL("moe", llm_moe_route, (const float *)logits.data, (long long)logits.ld, (int)logits.rows, n_experts, top, score,
+           renormalize ? 1 : 0, chosen, weight, s);
+}
+int moe_tile_rows() {
+  static auto f = resolve<int (*)()>("moe", "llm_moe_tile_rows");
+  return f();
+}
+void moe_sort(const int *chosen, int n_rows, int n_experts, int *offsets, int *perm, int *tiles, cudaStream_t s) {
+  LLM_CALL("moe", llm_moe_sort, chosen, n_rows, n_experts, moe_tile_rows(), offsets, perm, tiles, s);
+}
+void moe_rows(const Act &x, const void *up, const void *down, const int *chosen, const float *weight, int top, int width, int ff,
+              int act, bool weight_on_output, float *out, cudaStream_t s) {
+  LLM_CALL("moe", llm_moe_rows, code(x.dtype), x.data, (long long)x.ld, up, down, chosen, weight, (int)x.rows, top, width, ff, act,
+           weight_on_output ? 1 : 0, out, s);
+}
+bool moe_grouped_supported(int width, int ff) {
+  static auto f = resolve<int (*)(int, int)>("moe", "llm_moe_grouped_supports");
+  return f(width, ff) != 0;
+}
+void moe_grouped(const Act &x, const void *up, const void *down, const int *offsets, const int *perm, const int *tiles,
+                 const float *weight, int n_experts, int top, int width, int ff, int act, bool weight_on_output, void *mid,
+                 float *out, cudaStream_t s) {
+  LLM_CALL("moe", llm_moe_grouped, x.data, (long long)x.ld, up, down, offsets, perm, tiles, weight, (int)x.rows, n_experts, top,
+           width, ff, act, weight_on_output ? 1 : 0, mid, out, s);
 }
 
 // ---------------------------------------------------------------- sampling

@@ -34,6 +34,8 @@ void add_rmsnorm(float *resid, const Act *delta, const float *weight, float eps,
 // out[i] = resid[rows[i]] + delta's parts at that row (32-bit)
 void gather_rows_add(const float *resid, const Act *delta, const int *rows, int n_rows, float *out, int hidden, cudaStream_t s);
 void swiglu(const Act &gu, void *out, DType out_dtype, cudaStream_t s);
+// out[t] = [resid[t] + delta's parts at t | other[t]] in out's type, [rows, 2 * hidden]
+void concat_stream(const float *resid, const Act *delta, const float *other, const Act &out, int hidden, cudaStream_t s);
 void scale_rows(float *x, long long n, float scale, cudaStream_t s);
 void logit_transform(float *logits, long long n, float scale, float softcap, cudaStream_t s);
 void random_fill(void *out, DType dtype, long long n, unsigned long long seed, int law, float a, float b, cudaStream_t s);
@@ -76,28 +78,52 @@ void gemv_bf16(const Act &x, const Weight &w, const Act &out, bool swiglu, cudaS
 void rope_cache_write(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, const float *table, int table_rows,
                       int rot_dim, const int *tok_seq, const int *tok_pos, const int *page_table, int pt_stride,
                       void *kcache, void *vcache, int page_size, bool write_cache, cudaStream_t s);
+// The same for rows [q | k | v (n_kv * dv) | ...] with an RMS norm over all of q and all of k before the
+// rotation (weights of n_heads * d and n_kv * d values; null: none) and values of width dv.
+void qk_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, int dv, const float *q_norm, const float *k_norm,
+              float eps, const float *table, int table_rows, int rot_dim, const int *tok_seq, const int *tok_pos,
+              const int *page_table, int pt_stride, void *kcache, void *vcache, int page_size, bool write_cache, cudaStream_t s);
 // ---- attention
+// Masks: `window` > 0, a query sees the last `window` keys; `block` > 0, only keys of its own block
+// of `block` positions counted from 0.  `gate` (32-bit, one value per token and head, row stride
+// gate_stride; null: none): the head's result is multiplied by sigmoid(gate).
 void attention_generic(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_seq, const int *tok_pos,
-                       const int *page_table, int pt_stride, int n_heads, int n_kv, int d, int page_size, int window,
-                       float scale, cudaStream_t s);
+                       const int *page_table, int pt_stride, int n_heads, int n_kv, int d, int dv, int page_size, int window,
+                       int block, float scale, const float *gate, long long gate_stride, cudaStream_t s);
 bool attention_decode_supported(int d, int group);
 void attention_decode(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                       int pt_stride, int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window,
-                      float scale, float *ws_o, float *ws_ml, cudaStream_t s);
+                      int block, float scale, float *ws_o, float *ws_ml, cudaStream_t s);
 bool attention_decode_tc_supported(int d, int page_size, int group);
 int attention_decode_tc_ctas_per_sm(int d);
 void attention_decode_tc(const Act &qkv, const float *table, int table_rows, int rot_dim, const int *tok_pos,
                          const int *page_table, int pt_stride, void *kc, void *vc, bool write_cache, int n_seqs, int n_heads,
-                         int n_kv, int d, int page_size, int chunk, int max_len, int n_splits, int window, float scale,
-                         float *ws_o, float *ws_ml, int *counters, const Act &out, cudaStream_t s);
+                         int n_kv, int d, int page_size, int chunk, int max_len, int n_splits, int window, int block,
+                         float scale, float *ws_o, float *ws_ml, int *counters, const Act &out, cudaStream_t s);
 bool attention_prefill_supported(int d, int page_size);
 void attention_prefill(const Act &q, const Act &out, const void *kc, const void *vc, const int *seq_start, const int *seq_past,
                        const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int d,
-                       int page_size, int window, float scale, cudaStream_t s);
+                       int page_size, int window, int block, float scale, cudaStream_t s);
 bool attention_prefill_tc_supported(int d, int page_size);
 void attention_prefill_tc(const Act &q, const Act &out, const void *kc, const void *vc, long long n_pages, const int *seq_start,
                           const int *seq_past, const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads,
-                          int n_kv, int d, int page_size, int window, float scale, int *status, cudaStream_t s);
+                          int n_kv, int d, int page_size, int window, int block, float scale, int *status, cudaStream_t s);
+// out[t, h, :] *= sigmoid(gate[t * gate_stride + h]) for heads of width dv
+void head_gate(const Act &out, const float *gate, long long gate_stride, int n_heads, int dv, cudaStream_t s);
+// ---- routed feed-forward (csrc/moe.cu)
+enum Activation { GeluErf = 0, GeluTanh = 1, Silu = 2 };
+void activation(const Act &in, const Act &out, int act, cudaStream_t s);
+// logits [T, E] 32-bit -> chosen [T * top], weight [T * top]; score 0 sigmoid, 1 softmax
+void moe_route(const Act &logits, int n_experts, int top, int score, bool renormalize, int *chosen, float *weight, cudaStream_t s);
+int moe_tile_rows();
+void moe_sort(const int *chosen, int n_rows, int n_experts, int *offsets, int *perm, int *tiles, cudaStream_t s);
+// x [T, width]; up [E, ff, width], down [E, width, ff] in x's type; out [top, T, width] 32-bit
+void moe_rows(const Act &x, const void *up, const void *down, const int *chosen, const float *weight, int top, int width, int ff,
+              int act, bool weight_on_output, float *out, cudaStream_t s);
+bool moe_grouped_supported(int width, int ff);
+void moe_grouped(const Act &x, const void *up, const void *down, const int *offsets, const int *perm, const int *tiles,
+                 const float *weight, int n_experts, int top, int width, int ff, int act, bool weight_on_output, void *mid,
+                 float *out, cudaStream_t s);
 // ---- sampling
 void argmax(const float *logits, long long stride, int n_rows, int vocab, int *out, cudaStream_t s);
 void sample(const float *logits, long long stride, int n_rows, int vocab, float temperature, int top_k, float top_p,

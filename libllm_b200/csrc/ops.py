@@ -192,18 +192,96 @@ def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, n_heads: int, n_kv:
 def attention_generic(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                       tok_seq: torch.Tensor, tok_pos: torch.Tensor, page_table: torch.Tensor,
                       n_heads: int, n_kv: int, head_dim: int, page_size: int, window: Optional[int],
-                      scale: float) -> torch.Tensor:
-    """q is a [T, >= n_heads*d] view whose first n_heads*d columns are the rotated queries."""
-    _on_gpu(q, out, kcache, vcache, tok_seq, tok_pos, page_table)
+                      scale: float, v_head_dim: Optional[int] = None, block: Optional[int] = None,
+                      gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q is a [T, >= n_heads*d] view whose first n_heads*d columns are the rotated queries.  Values
+    may have a width of their own; ``block``: a query sees only the keys of its own block of that
+    many positions; ``gate`` [T, >= n_heads] 32-bit: head results are multiplied by sigmoid(gate)."""
+    _on_gpu(q, out, kcache, vcache, tok_seq, tok_pos, page_table, gate)
     T = q.shape[0]
-    assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == T and out.shape[1] == n_heads * head_dim
+    dv = int(v_head_dim or head_dim)
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == T and out.shape[1] == n_heads * dv
     assert kcache.dtype == q.dtype and out.dtype == q.dtype
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == T
     _call("attention_generic", "llm_attention_generic",
           [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
-           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_longlong, c_void_p],
           dtype_code(q.dtype), _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
-          _ptr(tok_seq), _ptr(tok_pos), _ptr(page_table), page_table.stride(0), T, n_heads, n_kv, head_dim,
-          page_size, int(window or 0), float(scale), _stream())
+          _ptr(tok_seq), _ptr(tok_pos), _ptr(page_table), page_table.stride(0), T, n_heads, n_kv, head_dim, dv,
+          page_size, int(window or 0), int(block or 0), float(scale), _ptr(gate), gate.stride(0) if gate is not None else 0,
+          _stream())
+    return out
+
+
+def qk_place(qkv: torch.Tensor, q_out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, v_head_dim: int,
+             q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float, table: Optional[torch.Tensor],
+             tok_seq: torch.Tensor, tok_pos: torch.Tensor, page_table: torch.Tensor, kcache: torch.Tensor,
+             vcache: torch.Tensor, page_size: int, write_cache: bool = True) -> None:
+    """Rows [q | k | v | ...]: RMS norm over all of q and all of k (weights or None), rotation of the
+    first ``table.shape[1]`` channels of each head, q to ``q_out``, k and v to the paged cache."""
+    _on_gpu(qkv, q_out, q_norm, k_norm, table, tok_seq, tok_pos, page_table, kcache, vcache)
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1 and q_out.stride(1) == 1
+    _call("rope", "llm_qk_place",
+          [c_int, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+           c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+          dtype_code(qkv.dtype), dtype_code(q_out.dtype), _ptr(qkv), qkv.stride(0), _ptr(q_out), q_out.stride(0), T, n_heads,
+          n_kv, head_dim, v_head_dim, _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(table),
+          table.shape[0] if table is not None else 0, table.shape[1] if table is not None else 0, _ptr(tok_seq),
+          _ptr(tok_pos), _ptr(page_table), page_table.stride(0), _ptr(kcache), _ptr(vcache), page_size,
+          1 if write_cache else 0, _stream())
+
+
+# ------------------------------------------------------------------ routed feed-forward
+ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def moe_route(logits: torch.Tensor, top: int, score: str = "sigmoid", renormalize: bool = False):
+    """(chosen [T, top] int32, weight [T, top] float32) from 32-bit router logits [T, E]."""
+    _on_gpu(logits)
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    chosen = torch.empty(T, top, dtype=torch.int32, device=logits.device)
+    weight = torch.empty(T, top, dtype=torch.float32, device=logits.device)
+    _call("moe", "llm_moe_route", [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+          _ptr(logits), logits.stride(0), T, E, top, {"sigmoid": 0, "softmax": 1}[score], 1 if renormalize else 0,
+          _ptr(chosen), _ptr(weight), _stream())
+    return chosen, weight
+
+
+def moe_experts(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
+                act: str = "gelu", weight_on: str = "input", grouped: bool = False) -> torch.Tensor:
+    """out [top, T, width] 32-bit: the chosen experts' down(act(up(x))), a row per choice.  up [E, ff, width],
+    down [E, width, ff].  ``grouped``: rows sorted by expert and multiplied on the tensor cores (bfloat16)."""
+    _on_gpu(x, up, down, chosen, weight)
+    T, width = x.shape
+    E, ff = up.shape[0], up.shape[1]
+    top = chosen.shape[1]
+    assert up.is_contiguous() and down.is_contiguous() and x.stride(1) == 1 and up.dtype == x.dtype == down.dtype
+    assert tuple(down.shape) == (E, width, ff) and chosen.is_contiguous() and weight.is_contiguous()
+    out = torch.empty(top, T, width, dtype=torch.float32, device=x.device)
+    if not grouped:
+        _call("moe", "llm_moe_rows", [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                      c_int, c_int, c_int, c_void_p, c_void_p],
+              dtype_code(x.dtype), _ptr(x), x.stride(0), _ptr(up), _ptr(down), _ptr(chosen), _ptr(weight), T, top, width, ff,
+              ACTIVATIONS[act], 1 if weight_on == "output" else 0, _ptr(out), _stream())
+        return out
+    assert x.dtype == torch.bfloat16
+    lib = build.load("moe")
+    lib.llm_moe_tile_rows.restype = c_int
+    tile = lib.llm_moe_tile_rows()
+    n_rows = T * top
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=x.device)
+    perm = torch.empty(n_rows, dtype=torch.int32, device=x.device)
+    tiles = torch.empty(1 + 2 * (min(E, n_rows) + n_rows // tile), dtype=torch.int32, device=x.device)
+    mid = torch.empty(n_rows, ff, dtype=torch.bfloat16, device=x.device)
+    _call("moe", "llm_moe_sort", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+          _ptr(chosen), n_rows, E, tile, _ptr(offsets), _ptr(perm), _ptr(tiles), _stream())
+    _call("moe", "llm_moe_grouped", [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                     c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+          _ptr(x), x.stride(0), _ptr(up), _ptr(down), _ptr(offsets), _ptr(perm), _ptr(tiles), _ptr(weight), T, E, top, width,
+          ff, ACTIVATIONS[act], 1 if weight_on == "output" else 0, _ptr(mid), _ptr(out), _stream())
     return out
 
 
@@ -276,7 +354,7 @@ def attention_decode_supported(head_dim: int, group: int) -> bool:
 def attention_decode(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                      tok_pos: torch.Tensor, page_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
                      page_size: int, chunk: int, n_splits: int, window: Optional[int], scale: float,
-                     ws_o: Optional[torch.Tensor], ws_ml: Optional[torch.Tensor]) -> torch.Tensor:
+                     ws_o: Optional[torch.Tensor], ws_ml: Optional[torch.Tensor], block: Optional[int] = None) -> torch.Tensor:
     """One query token per sequence over the paged cache, keys split into ``n_splits``
     runs of ``chunk``; ``ws_o``/``ws_ml`` are the scratch the splits are joined through."""
     _on_gpu(q, out, kcache, vcache, tok_pos, page_table, ws_o, ws_ml)
@@ -288,10 +366,10 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, v
         assert ws_ml.dtype == torch.float32 and ws_ml.numel() >= B * n_heads * n_splits * 2
     _call("attention_decode", "llm_attention_decode",
           [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p],
+           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p],
           _ptr(q), q.stride(0) if B > 1 else q.shape[1], _ptr(out), out.stride(0) if B > 1 else out.shape[1],
           _ptr(kcache), _ptr(vcache), _ptr(tok_pos), _ptr(page_table), page_table.stride(0), B, n_heads, n_kv,
-          head_dim, page_size, chunk, n_splits, int(window or 0), float(scale), _ptr(ws_o), _ptr(ws_ml), _stream())
+          head_dim, page_size, chunk, n_splits, int(window or 0), int(block or 0), float(scale), _ptr(ws_o), _ptr(ws_ml), _stream())
     return out
 
 
@@ -306,7 +384,7 @@ def attention_prefill_supported(head_dim: int, page_size: int) -> bool:
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                       seq_start: torch.Tensor, seq_past: torch.Tensor, page_table: torch.Tensor, n_seqs: int,
                       max_q_len: int, n_heads: int, n_kv: int, head_dim: int, page_size: int,
-                      window: Optional[int], scale: float) -> torch.Tensor:
+                      window: Optional[int], scale: float, block: Optional[int] = None) -> torch.Tensor:
     """Causal attention of every sequence's new tokens (rows seq_start[b]..seq_start[b+1]-1 of
     ``q``, standing behind seq_past[b] cached tokens) over the paged cache, which already
     holds the new tokens' keys and values."""
@@ -319,10 +397,10 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, 
     assert tuple(kcache.shape[1:]) == (n_kv, page_size, head_dim)
     _call("attention_prefill", "llm_attention_prefill",
           [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
           _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(seq_start),
           _ptr(seq_past), _ptr(page_table), page_table.stride(0), n_seqs, max_q_len, n_heads, n_kv, head_dim,
-          page_size, int(window or 0), float(scale), _stream())
+          page_size, int(window or 0), int(block or 0), float(scale), _stream())
     return out
 
 
@@ -447,7 +525,7 @@ def attention_decode_tc(qkv: torch.Tensor, out: torch.Tensor, table: torch.Tenso
                         n_kv: int, head_dim: int, page_size: int, chunk: int, n_splits: int, window: Optional[int],
                         scale: float, write_cache: bool, ws_o: Optional[torch.Tensor],
                         ws_ml: Optional[torch.Tensor], counters: Optional[torch.Tensor],
-                        max_len: int = 0) -> torch.Tensor:
+                        max_len: int = 0, block: Optional[int] = None) -> torch.Tensor:
     """One token per sequence: rotates q and k of the 32-bit stacked rows ``qkv``, appends k and v to
     the cache (with ``write_cache``), attends over the cache and joins the key splits, in one launch.
     ``counters`` (int32, one per sequence and kv head) must be zero before the first launch; the
@@ -473,12 +551,12 @@ def attention_decode_tc(qkv: torch.Tensor, out: torch.Tensor, table: torch.Tenso
         assert counters.dtype == torch.int32 and counters.numel() >= B * n_kv
     _call("attention_decode_tc", "llm_attention_decode_tc",
           [c_void_p, c_longlong, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
-           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
            c_void_p, c_void_p, c_longlong, c_void_p],
           _ptr(qkv), qkv2.stride(0) if B > 1 else qkv2.shape[1], parts, part_stride, _ptr(table), table.shape[0],
           table.shape[1],
           _ptr(tok_pos), _ptr(page_table), page_table.stride(0), _ptr(kcache), _ptr(vcache), 1 if write_cache else 0,
-          B, n_heads, n_kv, head_dim, page_size, chunk, int(max_len), n_splits, int(window or 0), float(scale),
+          B, n_heads, n_kv, head_dim, page_size, chunk, int(max_len), n_splits, int(window or 0), int(block or 0), float(scale),
           _ptr(ws_o), _ptr(ws_ml), _ptr(counters), _ptr(out), out.stride(0) if B > 1 else out.shape[1], _stream())
     return out
 
@@ -494,7 +572,7 @@ def attention_prefill_tc_supported(head_dim: int, page_size: int) -> bool:
 def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                          seq_start: torch.Tensor, seq_past: torch.Tensor, page_table: torch.Tensor, n_seqs: int,
                          max_q_len: int, n_heads: int, n_kv: int, head_dim: int, page_size: int,
-                         window: Optional[int], scale: float, form: int = 0) -> torch.Tensor:
+                         window: Optional[int], scale: float, form: int = 0, block: Optional[int] = None) -> torch.Tensor:
     """The same attention as ``attention_prefill`` with both products on tcgen05 (head sizes 64, 128).
     ``form``: 1 for CTAs of 128 query rows and tiles of 64 keys, 2 for CTAs of 256 rows and tiles of
     128 keys, 0 for the library's choice (the second when a sequence brings more than 128 rows)."""
@@ -505,8 +583,8 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
     assert kcache.is_contiguous() and vcache.is_contiguous() and tuple(kcache.shape[1:]) == (n_kv, page_size, head_dim)
     _call("attention_prefill_tc", "llm_attention_prefill_tc",
           [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
-           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
           _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), kcache.shape[0],
           _ptr(seq_start), _ptr(seq_past), _ptr(page_table), page_table.stride(0), n_seqs, max_q_len, n_heads, n_kv,
-          head_dim, page_size, int(window or 0), float(scale), int(form), _ptr(tc_status(q.device)), _stream())
+          head_dim, page_size, int(window or 0), int(block or 0), float(scale), int(form), _ptr(tc_status(q.device)), _stream())
     return out

@@ -153,3 +153,110 @@ LLM_EXPORT int llm_rope_cache_write(int in_dtype, int dtype, const void *qkv, lo
   LLM_CHECK_LAUNCH("rope_cache_write");
   return LLM_OK;
 }
+
+// ---------------------------------------------------------------- norm of the whole projection + rotation + append
+// For mixers that normalise their queries and keys before the rotation, and for values of another
+// width than the keys.  A row of the stacked product is [q: n_heads * d | k: n_kv * d | v: n_kv * dv |
+// anything else]; one CTA serves one token:
+//   q <- q / sqrt(mean(q^2) + eps) * q_norm   over all n_heads * d channels at once (likewise k)
+//   rotation of the first rot_dim channels of every q and k head (pairs i, i + rot_dim/2)
+//   q -> q_out, k and v -> the token's row of the paged cache ([pages, kv_heads, page_size, d or dv]).
+// Norm weights may be null (no norm) and rot_dim 0 (no rotation).  Sums, factors and angles are
+// 32-bit; a sum's order is fixed by the thread count, not by the batch.
+template <typename TI, typename T>
+__global__ void __launch_bounds__(256)
+qk_place_kernel(const TI *__restrict__ qkv, long long row_stride, T *__restrict__ q_out, long long q_stride,
+                int n_heads, int n_kv, int d, int dv, const float *__restrict__ q_norm,
+                const float *__restrict__ k_norm, float eps, const float *__restrict__ table, int table_rows,
+                int rot_dim, const int *__restrict__ tok_seq, const int *__restrict__ tok_pos,
+                const int *__restrict__ page_table, int pt_stride, T *__restrict__ kcache,
+                T *__restrict__ vcache, int page_size, int write_cache) {
+  __shared__ float scratch[256 / 32 + 1];
+  grid_dependents_launch();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  const TI *row = qkv + (size_t)t * row_stride;
+  const int qw = n_heads * d, kw = n_kv * d;
+  float q_fac = 1.f, k_fac = 1.f;
+  if (q_norm) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < qw; c += 256) {
+      const float v = to_float(row[c]);
+      ss = fmaf(v, v, ss);
+    }
+    q_fac = 1.f / sqrtf(block_sum<256>(ss, scratch) / (float)qw + eps);
+  }
+  if (k_norm && write_cache) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < kw; c += 256) {
+      const float v = to_float(row[qw + c]);
+      ss = fmaf(v, v, ss);
+    }
+    k_fac = 1.f / sqrtf(block_sum<256>(ss, scratch) / (float)kw + eps);
+  }
+  size_t cache_row = 0;
+  if (write_cache) {
+    const int page = page_table[(size_t)tok_seq[t] * pt_stride + pos / page_size];
+    cache_row = (size_t)page * n_kv * page_size + (pos % page_size);
+  }
+  const int half = rot_dim / 2;
+  const float *cs = table ? table + (size_t)(pos < table_rows ? pos : table_rows - 1) * rot_dim : nullptr;
+  const int per_head = d - half;               // `half` pairs, then the channels that are not rotated
+  const int n_rot = (n_heads + (write_cache ? n_kv : 0)) * per_head;
+  for (int item = threadIdx.x; item < n_rot; item += 256) {
+    const int slot = item / per_head, i = item - slot * per_head;
+    const bool is_q = slot < n_heads;
+    const TI *src = row + (size_t)slot * d;
+    const float *nw = is_q ? (q_norm ? q_norm + (size_t)slot * d : nullptr) : (k_norm ? k_norm + (size_t)(slot - n_heads) * d : nullptr);
+    const float fac = is_q ? q_fac : k_fac;
+    T *dst = is_q ? q_out + (size_t)t * q_stride + (size_t)slot * d
+                  : kcache + (cache_row + (size_t)(slot - n_heads) * page_size) * d;
+    if (i < half) {
+      float a = to_float(src[i]) * fac, b = to_float(src[i + half]) * fac;
+      if (nw) {
+        a *= nw[i];
+        b *= nw[i + half];
+      }
+      const float c = cs[i], s = cs[half + i];
+      dst[i] = from_float<T>(a * c - b * s);
+      dst[i + half] = from_float<T>(b * c + a * s);
+    } else {
+      const int ch = i + half;
+      float a = to_float(src[ch]) * fac;
+      if (nw) a *= nw[ch];
+      dst[ch] = from_float<T>(a);
+    }
+  }
+  if (write_cache) {
+    const TI *vsrc = row + qw + kw;
+    for (int item = threadIdx.x; item < n_kv * dv; item += 256) {
+      const int kvh = item / dv, ch = item - kvh * dv;
+      vcache[(cache_row + (size_t)kvh * page_size) * dv + ch] = from_float<T>(to_float(vsrc[item]));
+    }
+  }
+}
+
+LLM_EXPORT int llm_qk_place(int in_dtype, int dtype, const void *qkv, long long row_stride, void *q_out,
+                            long long q_stride, int n_tokens, int n_heads, int n_kv, int d, int dv,
+                            const float *q_norm, const float *k_norm, float eps, const float *table,
+                            int table_rows, int rot_dim, const int *tok_seq, const int *tok_pos,
+                            const int *page_table, int pt_stride, void *kcache, void *vcache, int page_size,
+                            int write_cache, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && d > 0 && dv > 0, "qk_place: bad sizes");
+  LLM_REQUIRE(rot_dim % 2 == 0 && rot_dim <= d && rot_dim >= 0 && (rot_dim == 0 || table != nullptr),
+              "qk_place: rotated width %d does not fit head size %d", rot_dim, d);
+  LLM_REQUIRE(row_stride >= (long long)n_heads * d + (long long)n_kv * (d + dv), "qk_place: the stacked rows are too short");
+#define QK_PLACE(TI, T)                                                                                          \
+  llm_launch(qk_place_kernel<TI, T>, dim3(n_tokens), dim3(256), 0, stream, (const TI *)qkv, row_stride, (T *)q_out, \
+             q_stride, n_heads, n_kv, d, dv, q_norm, k_norm, eps, table, table_rows, rot_dim, tok_seq, tok_pos,  \
+             page_table, pt_stride, (T *)kcache, (T *)vcache, page_size, write_cache)
+  if (in_dtype == LLM_F32 && dtype == LLM_F32) QK_PLACE(float, float);
+  else if (in_dtype == LLM_F32 && dtype == LLM_BF16) QK_PLACE(float, __nv_bfloat16);
+  else if (in_dtype == LLM_BF16 && dtype == LLM_BF16) QK_PLACE(__nv_bfloat16, __nv_bfloat16);
+  else LLM_FAIL("qk_place: unsupported dtypes in %d out %d", in_dtype, dtype);
+#undef QK_PLACE
+  LLM_CHECK_LAUNCH("qk_place");
+  return LLM_OK;
+}

@@ -76,6 +76,7 @@ Model::Model(ModelSpec spec, Json config, DType dtype, int64_t max_positions, in
       LLM_THROW(Config, "schedule entry %zu names layer %d, the model has %zu", i, e.layer, layers_.size());
     if (e.cache_from >= (int)i)
       LLM_THROW(Config, "schedule entry %zu reads the cache of entry %d, which does not run before it", i, e.cache_from);
+    if (!e.input_mix.empty()) input_mixes_[e.input_mix];
   }
 }
 
@@ -85,6 +86,7 @@ std::vector<TensorNeed> Model::tensor_needs() const {
   for (const auto &l : layers_)
     for (auto &n : l->tensor_needs()) needs.push_back(n);
   for (auto &n : final_norm_->tensor_needs()) needs.push_back(n);
+  for (const auto &kv : input_mixes_) needs.push_back({kv.first, {spec_.hidden, 2 * spec_.hidden}});
   if (!spec_.head.empty()) needs.push_back({spec_.head, {spec_.vocab_size, spec_.hidden}});
   return needs;
 }
@@ -109,6 +111,7 @@ void Model::load_with(const Loader &loader) {
   embedding_ = loader.fetch(needs.front());
   for (auto &l : layers_) l->load(loader);
   final_norm_->load(loader);
+  for (auto &kv : input_mixes_) kv.second = loader.fetch({kv.first, {spec_.hidden, 2 * spec_.hidden}});
   if (spec_.head.empty()) {
     head_ = &embedding_;
   } else {
@@ -153,6 +156,23 @@ std::vector<std::vector<StateNeed>> Model::state_needs() const {
   return out;
 }
 
+// x <- W [x; x0]: the stream (with what is still to be added to it) beside the token rows, in the
+// engine's type, through the matrix; the product's 32-bit result is the new stream.
+void Model::mix_input(StepContext &ctx, ResidualStream &stream, const float *x0, const Weight &w) {
+  flush_chain(ctx);
+  const int64_t T = stream.rows, H = stream.hidden;
+  if (stream.pending.data && stream.pending.dtype != DType::F32) {
+    kernels::add_rmsnorm(stream.resid, &stream.pending, nullptr, 0.f, nullptr, ctx.dtype, nullptr, (int)T, (int)H, ctx.stream);
+    stream.pending = Act();
+  }
+  Act both = ctx.arena->act(ctx.dtype, T, 2 * H);
+  kernels::concat_stream(stream.resid, stream.pending.data ? &stream.pending : nullptr, x0, both, (int)H, ctx.stream);
+  stream.pending = Act();
+  Act y = linear(ctx, both, w, nullptr, DType::F32);
+  flush_chain(ctx);
+  LLM_CUDA(cudaMemcpyAsync(stream.resid, y.data, sizeof(float) * (size_t)(T * H), cudaMemcpyDeviceToDevice, ctx.stream));
+}
+
 Act Model::forward(StepContext &ctx, KVCache &cache, const std::vector<const int *> &tables, int table_width,
                    const int *fed_tokens, const int *fed_rows) {
   if (!loaded_) LLM_THROW(InvalidArg, "the model has no weights yet");
@@ -161,6 +181,11 @@ Act Model::forward(StepContext &ctx, KVCache &cache, const std::vector<const int
   kernels::embedding(embedding_.dtype, embedding_.data(), ctx.tokens, fed_tokens, fed_rows, resid, (int)T, (int)H,
                      (int)spec_.vocab_size, ctx.stream);
   if (spec_.embedding_scale != 1.0) kernels::scale_rows(resid, T * H, (float)spec_.embedding_scale, ctx.stream);
+  float *x0 = nullptr;                       // the token rows, kept for the runs that mix them in again
+  if (!input_mixes_.empty()) {
+    x0 = ctx.arena->alloc_n<float>((size_t)(T * H));
+    LLM_CUDA(cudaMemcpyAsync(x0, resid, sizeof(float) * (size_t)(T * H), cudaMemcpyDeviceToDevice, ctx.stream));
+  }
   ResidualStream stream;
   stream.resid = resid;
   stream.rows = T;
@@ -172,6 +197,7 @@ Act Model::forward(StepContext &ctx, KVCache &cache, const std::vector<const int
       ctx.arena = ctx.layer_arenas[i & 1];
       ctx.arena->reset();
     }
+    if (!e.input_mix.empty()) mix_input(ctx, stream, x0, input_mixes_.at(e.input_mix));
     const bool last = i + 1 == spec_.schedule.size();
     ctx.rows_read_after = last && ctx.n_want > 0 && ctx.n_want < ctx.n_tokens ? ctx.want_rows : nullptr;
     ctx.n_rows_read_after = ctx.rows_read_after ? ctx.n_want : 0;
@@ -199,9 +225,7 @@ Act Model::forward(StepContext &ctx, KVCache &cache, const std::vector<const int
 }
 
 std::unique_ptr<Model> model_from_config(const Json &config_json, DType dtype, int64_t max_positions) {
-  if (!config_json.is_object() || !config_json.get("model_type").is_string())
-    LLM_THROW(Config, "config.json: required key 'model_type' is missing");
-  const Architecture &arch = architecture_for(config_json.get("model_type").as_string());
+  const Architecture &arch = architecture_for(architecture_name(config_json, "config.json"));
   Json normal = arch.parse(config_json);
   ModelSpec spec = arch.describe(normal);
   return std::unique_ptr<Model>(new Model(std::move(spec), std::move(normal), dtype, max_positions));

@@ -67,6 +67,8 @@ class Model {
   std::vector<std::unique_ptr<Block>> layers_;
   std::unique_ptr<Norm> final_norm_;
   Weight embedding_, head_own_;
+  std::map<std::string, Weight> input_mixes_;      // ScheduleEntry::input_mix -> [hidden, 2 * hidden]
+  void mix_input(StepContext &ctx, ResidualStream &stream, const float *x0, const Weight &w);
   const Weight *head_ = nullptr;
   bool loaded_ = false;
 };

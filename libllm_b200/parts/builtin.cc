@@ -151,6 +151,15 @@ class RotaryEmbedding : public PositionEncoding {
 // (src/libllm/llama.cc:178-225).  The stacked matrix is [Wq; Wk; Wv] as the reference's exporter
 // builds it (tools/llama_exporter.py:64-71), made here when the weights are loaded.  The position
 // part owns the rotation; without one, queries and keys are used as they come.
+//
+// Options beyond the reference's attention, each a key of the description:
+//   v_head_dim   values (and the heads' results) of another width than queries and keys
+//   qk_norm      {q, k, eps}: an RMS norm over the whole q projection and the whole k projection
+//                (weights of n_heads * head_dim and n_kv_heads * head_dim values) before the rotation
+//   block        a query sees only the keys of its own block of `block` positions, counted from
+//                position 0 of the sequence (a chunked mask); the cache gives earlier pages back
+//   head_gate    a matrix [n_heads, hidden]: head h's result is multiplied by sigmoid(gate x)_h
+//                before the output projection; its rows ride at the end of the stacked product
 class Attention : public Mixer {
  public:
   Attention(const Json &spec, const BuildEnv &env) : Mixer(spec, env) {
@@ -167,19 +176,33 @@ class Attention : public Mixer {
     v_name_ = r.string("v");
     o_name_ = r.string("o");
     if (n_heads_ % n_kv_) LLM_THROW(Config, "attention: %d heads are not a multiple of %d groups", n_heads_, n_kv_);
-    if (d_ % 16 || d_ < 16 || d_ > 256)
-      LLM_THROW(Unsupported, "attention: head size %d is not supported (multiples of 16 from 16 to 256)", d_);
-    if (r.integer_or("v_head_dim", d_) != d_)
-      LLM_THROW(Unsupported, "attention: values of another width than the keys (%lld against %d) are not built",
-                (long long)r.integer("v_head_dim"), d_);
+    dv_ = (int)r.integer_or("v_head_dim", d_);
+    if (d_ > 256 || dv_ > 256) LLM_THROW(Unsupported, "attention: head sizes %d / %d are not supported (up to 256)", d_, dv_);
+    block_ = (int)r.integer_or("block", 0, 0);
+    if (r.present("qk_norm")) {
+      ConfigReader n(r.object("qk_norm"), "attention description: qk_norm");
+      q_norm_name_ = n.string("q");
+      k_norm_name_ = n.string("k");
+      qk_eps_ = (float)n.number("eps");
+    }
+    gate_name_ = r.string_or("head_gate", "");
+    if (bias_ && (!gate_name_.empty() || !q_norm_name_.empty()))
+      LLM_THROW(Unsupported, "attention: a bias together with a head gate or a q/k norm is not built");
     if (!spec.get("position").is_null()) position_ = build_as<PositionEncoding>("position", spec.get("position"), env);
     q_width_ = (int64_t)n_heads_ * d_;
     kv_width_ = (int64_t)n_kv_ * d_;
+    v_width_ = (int64_t)n_kv_ * dv_;
+    o_width_ = (int64_t)n_heads_ * dv_;
+    gate_offset_ = q_width_ + kv_width_ + v_width_;
+    // rows of the stacked matrix: a multiple of 8, so that rows of the 32-bit product start on 32 bytes
+    stacked_rows_ = (gate_offset_ + (gate_name_.empty() ? 0 : n_heads_) + 7) / 8 * 8;
+    // what the kernels written for the reference's attention do not take (they get the general ones)
+    plain_ = dv_ == d_ && q_norm_name_.empty() && d_ % 16 == 0 && d_ >= 16;
   }
 
   std::vector<TensorNeed> tensor_needs() const override {
-    std::vector<TensorNeed> needs = {{q_name_, {q_width_, hidden_}}, {k_name_, {kv_width_, hidden_}}, {v_name_, {kv_width_, hidden_}},
-                                     {o_name_, {hidden_, q_width_}}};
+    std::vector<TensorNeed> needs = {{q_name_, {q_width_, hidden_}}, {k_name_, {kv_width_, hidden_}}, {v_name_, {v_width_, hidden_}},
+                                     {o_name_, {hidden_, o_width_}}};
     if (bias_)
       for (const auto &p : {std::make_pair(q_name_, q_width_), std::make_pair(k_name_, kv_width_), std::make_pair(v_name_, kv_width_)}) {
         std::string n = p.first;
@@ -187,6 +210,11 @@ class Attention : public Mixer {
         if (n.size() >= suffix.size() && n.compare(n.size() - suffix.size(), suffix.size(), suffix) == 0) n.resize(n.size() - suffix.size());
         needs.push_back({n + "bias", {p.second}, TensorRole::Vector, false});
       }
+    if (!q_norm_name_.empty()) {
+      needs.push_back({q_norm_name_, {q_width_}, TensorRole::Vector, false});
+      needs.push_back({k_norm_name_, {kv_width_}, TensorRole::Vector, false});
+    }
+    if (!gate_name_.empty()) needs.push_back({gate_name_, {(int64_t)n_heads_, hidden_}});
     if (position_)
       for (auto &n : position_->tensor_needs()) needs.push_back(n);
     return needs;
@@ -196,19 +224,26 @@ class Attention : public Mixer {
     const std::vector<TensorNeed> needs = tensor_needs();
     const size_t es = dtype_size(l.engine);
     w_qkv_.dtype = l.engine;
-    w_qkv_.rows = q_width_ + 2 * kv_width_;
+    w_qkv_.rows = stacked_rows_;
     w_qkv_.cols = hidden_;
-    w_qkv_.buf.allocate((size_t)w_qkv_.rows * (size_t)hidden_ * es);
+    w_qkv_.buf.allocate((size_t)w_qkv_.rows * (size_t)hidden_ * es, true);
     char *p = (char *)w_qkv_.buf.get();
     l.fetch_into(needs[0], l.engine, p);
     l.fetch_into(needs[1], l.engine, p + (size_t)q_width_ * hidden_ * es);
     l.fetch_into(needs[2], l.engine, p + (size_t)(q_width_ + kv_width_) * hidden_ * es);
     w_o_ = l.fetch(needs[3]);
+    size_t next = bias_ ? 7 : 4;
+    if (!q_norm_name_.empty()) {
+      q_norm_ = l.fetch(needs[next]);
+      k_norm_ = l.fetch(needs[next + 1]);
+      next += 2;
+    }
+    if (!gate_name_.empty()) l.fetch_into(needs[next], l.engine, p + (size_t)gate_offset_ * hidden_ * es);
     if (bias_) {
       b_qkv_.dtype = DType::F32;
       b_qkv_.rows = 1;
       b_qkv_.cols = w_qkv_.rows;
-      b_qkv_.buf.allocate((size_t)w_qkv_.rows * 4);
+      b_qkv_.buf.allocate((size_t)w_qkv_.rows * 4, true);
       float *b = b_qkv_.buf.as<float>();
       l.fetch_into(needs[4], DType::F32, b);
       l.fetch_into(needs[5], DType::F32, b + q_width_);
@@ -232,10 +267,13 @@ class Attention : public Mixer {
     if (env_.dtype != DType::BF16) return fams;
     const FastSwitches &f = fast_switches();
     const int group = n_heads_ / n_kv_;
+    if (!plain_) return fams;
+    if (!gate_name_.empty()) fams.push_back("elementwise");
     const bool tiled = env_.page_size == 64 && d_ % 16 == 0 && d_ >= 16 && d_ <= 128;
     if (f.prefill_attention_tc && env_.page_size == 64 && (d_ == 64 || d_ == 128)) fams.push_back("attention_prefill_tc");
     else if (f.prefill_attention && tiled) fams.push_back("attention_prefill");
-    if (f.decode_attention_tc && tiled && group <= 16 && !bias_ && position_) fams.push_back("attention_decode_tc");
+    if (f.decode_attention_tc && tiled && group <= 16 && !bias_ && position_ && gate_name_.empty())
+      fams.push_back("attention_decode_tc");
     else if (f.decode_attention && (d_ == 16 || d_ == 32 || d_ == 64 || d_ == 128) &&
              (group == 1 || group == 2 || group == 3 || group == 4 || group == 8))
       fams.push_back("attention_decode");
@@ -245,10 +283,13 @@ class Attention : public Mixer {
   bool wants_cache() const override { return true; }
   CacheNeed cache_need() const override {
     CacheNeed n;
-    n.kind = window_ > 0 ? "window" : "full";
+    // a mask of both kinds keeps everything: neither rule alone says which pages are done with
+    n.kind = window_ > 0 && block_ > 0 ? "full" : window_ > 0 ? "window" : block_ > 0 ? "block" : "full";
     n.n_kv_heads = n_kv_;
-    n.k_dim = n.v_dim = d_;
-    n.window = window_;
+    n.k_dim = d_;
+    n.v_dim = dv_;
+    n.window = n.kind == "window" ? window_ : 0;
+    n.block = n.kind == "block" ? block_ : 0;
     return n;
   }
 
@@ -260,7 +301,9 @@ class Attention : public Mixer {
     // the rotation, and the residual addition gets an unrounded term.
     int table_rows = 0, rot_dim = 0;
     const float *table = position_ ? position_->half_split_table(&table_rows, &rot_dim) : nullptr;
-    const bool fused = table && !bias_ && ctx.decode_only && f.decode_attention_tc && ctx.dtype == DType::BF16 &&
+    const bool has_gate = !gate_name_.empty();
+    const float *gate = nullptr;
+    const bool fused = plain_ && !has_gate && table && !bias_ && ctx.decode_only && f.decode_attention_tc && ctx.dtype == DType::BF16 &&
                        kernels::available("attention_decode_tc") && kernels::attention_decode_tc_supported(d_, cache->page_size, group);
     Act qkv = linear(ctx, x, w_qkv_, bias_ ? b_qkv_.buf.as<float>() : nullptr, DType::F32, fused);
     flush_chain(ctx);
@@ -285,20 +328,27 @@ class Attention : public Mixer {
       }
       kernels::attention_decode_tc(qkv, table, table_rows, rot_dim, ctx.tok_pos, cache->page_table, cache->table_width, cache->k,
                                    cache->v, cache->writes, ctx.n_seqs, n_heads_, n_kv_, d_, cache->page_size, 0, max_len, n_splits,
-                                   window_, scale_, ws_o, ws_ml, counters, out, ctx.stream);
+                                   window_, block_, scale_, ws_o, ws_ml, counters, out, ctx.stream);
       return linear(ctx, out, w_o_, nullptr, DType::F32, true);
     }
     Act q = ctx.arena->act(ctx.dtype, ctx.n_tokens, q_width_);
     const QkvLayout layout{n_heads_, n_kv_, d_};
-    if (position_) {
+    if (has_gate) gate = (const float *)qkv.data + gate_offset_;
+    if (!q_norm_name_.empty() || dv_ != d_) {
+      if (position_ && !table)
+        LLM_THROW(Unsupported, "attention: a q/k norm or values of another width need a position part with a half-split table (or none)");
+      kernels::qk_place(qkv, q, n_heads_, n_kv_, d_, dv_, q_norm_.buf.as<float>(), k_norm_.buf.as<float>(), qk_eps_, table, table_rows,
+                        rot_dim, ctx.tok_seq, ctx.tok_pos, cache->page_table, cache->table_width, cache->k, cache->v,
+                        cache->page_size, cache->writes, ctx.stream);
+    } else if (position_) {
       position_->rotate_and_store(ctx, qkv, q, layout, *cache);
     } else {
       kernels::rope_cache_write(qkv, q, n_heads_, n_kv_, d_, nullptr, 0, 0, ctx.tok_seq, ctx.tok_pos, cache->page_table,
                                 cache->table_width, cache->k, cache->v, cache->page_size, cache->writes, ctx.stream);
     }
-    Act out = ctx.arena->act(ctx.dtype, ctx.n_tokens, q_width_);
+    Act out = ctx.arena->act(ctx.dtype, ctx.n_tokens, o_width_);
     bool done = false;
-    if (ctx.dtype == DType::BF16) {
+    if (ctx.dtype == DType::BF16 && plain_) {
       if (ctx.decode_only && f.decode_attention && kernels::available("attention_decode") &&
           kernels::attention_decode_supported(d_, group)) {
         // enough CTAs to fill the GPU about eight times over at the longest length, runs of at
@@ -317,35 +367,36 @@ class Attention : public Mixer {
           ws_ml = ctx.arena->alloc_n<float>((size_t)ctx.n_seqs * n_heads_ * n_splits * 2);
         }
         kernels::attention_decode(q, out, cache->k, cache->v, ctx.tok_pos, cache->page_table, cache->table_width, n_heads_, n_kv_,
-                                  d_, cache->page_size, chunk, n_splits, window_, scale_, ws_o, ws_ml, ctx.stream);
+                                  d_, cache->page_size, chunk, n_splits, window_, block_, scale_, ws_o, ws_ml, ctx.stream);
         done = true;
       } else if (f.prefill_attention_tc && (d_ == 64 || d_ == 128) && kernels::available("attention_prefill_tc") &&
                  kernels::attention_prefill_tc_supported(d_, cache->page_size)) {
         kernels::attention_prefill_tc(q, out, cache->k, cache->v, cache->n_pages, ctx.seq_start, ctx.seq_past, cache->page_table,
                                       cache->table_width, ctx.n_seqs, ctx.max_q_len, n_heads_, n_kv_, d_, cache->page_size, window_,
-                                      scale_, ctx.tc_status, ctx.stream);
+                                      block_, scale_, ctx.tc_status, ctx.stream);
         done = true;
       } else if (f.prefill_attention && kernels::available("attention_prefill") &&
                  kernels::attention_prefill_supported(d_, cache->page_size)) {
         kernels::attention_prefill(q, out, cache->k, cache->v, ctx.seq_start, ctx.seq_past, cache->page_table, cache->table_width,
-                                   ctx.n_seqs, ctx.max_q_len, n_heads_, n_kv_, d_, cache->page_size, window_, scale_, ctx.stream);
+                                   ctx.n_seqs, ctx.max_q_len, n_heads_, n_kv_, d_, cache->page_size, window_, block_, scale_, ctx.stream);
         done = true;
       }
+      if (done && gate) kernels::head_gate(out, gate, qkv.ld, n_heads_, dv_, ctx.stream);
     }
     if (!done)
       kernels::attention_generic(q, out, cache->k, cache->v, ctx.tok_seq, ctx.tok_pos, cache->page_table, cache->table_width,
-                                 n_heads_, n_kv_, d_, cache->page_size, window_, scale_, ctx.stream);
+                                 n_heads_, n_kv_, d_, dv_, cache->page_size, window_, block_, scale_, gate, qkv.ld, ctx.stream);
     return linear(ctx, out, w_o_, nullptr, DType::F32, true);
   }
 
  private:
-  int64_t hidden_, q_width_, kv_width_;
-  int n_heads_, n_kv_, d_, window_;
-  bool bias_;
-  float scale_;
-  std::string q_name_, k_name_, v_name_, o_name_;
+  int64_t hidden_, q_width_, kv_width_, v_width_, o_width_, gate_offset_, stacked_rows_;
+  int n_heads_, n_kv_, d_, dv_, window_, block_;
+  bool bias_, plain_;
+  float scale_, qk_eps_ = 0.f;
+  std::string q_name_, k_name_, v_name_, o_name_, q_norm_name_, k_norm_name_, gate_name_;
   std::unique_ptr<PositionEncoding> position_;
-  Weight w_qkv_, w_o_, b_qkv_;
+  Weight w_qkv_, w_o_, b_qkv_, q_norm_, k_norm_;
 };
 
 // ---------------------------------------------------------------- SwiGLU
@@ -488,6 +539,95 @@ class PreNormBlock : public Block {
   std::unique_ptr<FeedForward> ff_;
 };
 
+// ---------------------------------------------------------------- parallel block
+// out = x + mixer(h) + ff(h) with h = norm(x): one norm, and both sublayers read its output.  The
+// feed-forward may be absent.  The mixer's result is added to the stream (by its own last product
+// where that can add as it stores, else by an addition pass) before the feed-forward's is left
+// pending for the next norm, since the stream carries one pending addition.
+class ParallelBlock : public Block {
+ public:
+  ParallelBlock(const Json &spec, const BuildEnv &env) : Block(spec, env) {
+    ConfigReader r = reader_of(spec, "parallel block");
+    norm_ = build_as<Norm>("norm", r.object("norm"), env);
+    mixer_ = build_as<Mixer>("mixer", r.object("mixer"), env);
+    if (r.present("ff")) ff_ = build_as<FeedForward>("feed_forward", r.object("ff"), env);
+  }
+  std::vector<Part *> parts() const {
+    std::vector<Part *> p = {norm_.get(), mixer_.get()};
+    if (ff_) p.push_back(ff_.get());
+    return p;
+  }
+  Mixer *mixer_part() override { return mixer_.get(); }
+  std::vector<TensorNeed> tensor_needs() const override {
+    std::vector<TensorNeed> out;
+    for (Part *p : parts())
+      for (auto &n : p->tensor_needs()) out.push_back(n);
+    return out;
+  }
+  void load(const Loader &l) override {
+    for (Part *p : parts()) p->load(l);
+  }
+  std::vector<std::string> kernel_families() const override {
+    std::vector<std::string> out = {"elementwise"};
+    for (Part *p : parts())
+      for (auto &f : p->kernel_families()) out.push_back(f);
+    return out;
+  }
+  bool capturable() const override {
+    for (Part *p : parts())
+      if (!p->capturable()) return false;
+    return true;
+  }
+  void forward(StepContext &ctx, ResidualStream &stream, LayerCache *cache, StateView *state) override {
+    auto sink = [&](bool on) {
+      ctx.residual_sink = on ? stream.resid : nullptr;
+      ctx.sink_rows = stream.rows;
+      ctx.sink_cols = stream.hidden;
+    };
+    Act h = norm_->forward(ctx, stream);
+    // the last layer of a prompt step: the feed-forward of the wanted rows alone, from their norms
+    const bool few = ff_ && ctx.rows_read_after && ctx.n_rows_read_after < stream.rows && !stream.picked;
+    Act h_few;
+    if (few) h_few = norm_->forward(ctx, stream, ctx.rows_read_after, ctx.n_rows_read_after);
+    sink(true);
+    Act r = mixer_->forward(ctx, h, cache, state);
+    sink(false);
+    stream.pending = r.data == (void *)stream.resid ? Act() : r;
+    if (ctx.nothing_read_after) {       // no logits wanted from this step: the stream is read by nobody
+      flush_chain(ctx);
+      stream.pending = Act();
+      return;
+    }
+    if (!ff_) return;
+    if (few) {
+      flush_chain(ctx);
+      const int64_t n = ctx.n_rows_read_after;
+      float *rows = ctx.arena->alloc_n<float>((size_t)(n * stream.hidden));
+      kernels::gather_rows_add(stream.resid, stream.pending.data ? &stream.pending : nullptr, ctx.rows_read_after, (int)n, rows,
+                               (int)stream.hidden, ctx.stream);
+      stream.resid = rows;
+      stream.rows = n;
+      stream.pending = Act();
+      stream.picked = true;
+      h = h_few;
+    } else if (stream.pending.data) {
+      flush_chain(ctx);
+      kernels::add_rmsnorm(stream.resid, &stream.pending, nullptr, 0.f, nullptr, ctx.dtype, nullptr, (int)stream.rows,
+                           (int)stream.hidden, ctx.stream);
+      stream.pending = Act();
+    }
+    sink(true);
+    r = ff_->forward(ctx, h);
+    sink(false);
+    stream.pending = r.data == (void *)stream.resid ? Act() : r;
+  }
+
+ private:
+  std::unique_ptr<Norm> norm_;
+  std::unique_ptr<Mixer> mixer_;
+  std::unique_ptr<FeedForward> ff_;
+};
+
 template <typename T>
 PartFactory factory_of() {
   return [](const Json &spec, const BuildEnv &env) { return std::unique_ptr<Part>(new T(spec, env)); };
@@ -497,7 +637,11 @@ PartFactory factory_of() {
 
 void register_part_raw(const std::string &category, const std::string &kind, PartFactory factory);   // parts/part.cc
 
+void register_feed_forward_parts();   // parts/feed_forward.cc
+
 void register_builtin_parts() {
+  register_part_raw("block", "parallel", factory_of<ParallelBlock>());
+  register_feed_forward_parts();
   register_part_raw("norm", "rmsnorm", factory_of<RMSNorm>());
   register_part_raw("position", "rope", factory_of<RotaryEmbedding>());
   register_part_raw("mixer", "attention", factory_of<Attention>());

@@ -1,0 +1,195 @@
+// Feed-forwards beyond the reference's SwiGLU: the two-matrix form with a choice of activation, and
+// the routed form (mixture of experts) over it.
+#include <algorithm>
+
+#include "config/config.h"
+#include "csrc/kernels.h"
+#include "parts/chain.h"
+#include "parts/linear.h"
+#include "parts/part.h"
+
+namespace llm {
+
+namespace {
+
+int activation_code(const std::string &name, const ConfigReader &r) {
+  if (name == "gelu") return kernels::GeluErf;          // 0.5 z (1 + erf(z / sqrt 2))
+  if (name == "gelu_tanh") return kernels::GeluTanh;    // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+  if (name == "silu") return kernels::Silu;
+  r.fail("activation '" + name + "' is not known (gelu, gelu_tanh, silu)");
+}
+
+// ---------------------------------------------------------------- up, activation, down
+// down(act(up x)), no biases; the activation in 32-bit on the product's 32-bit result.
+class Mlp : public FeedForward {
+ public:
+  Mlp(const Json &spec, const BuildEnv &env) : FeedForward(spec, env) {
+    ConfigReader r(spec, "mlp description");
+    hidden_ = r.integer("hidden");
+    inter_ = r.integer("intermediate");
+    act_ = activation_code(r.string_or("activation", "gelu"), r);
+    up_ = r.string("up");
+    down_ = r.string("down");
+  }
+  std::vector<TensorNeed> tensor_needs() const override { return {{up_, {inter_, hidden_}}, {down_, {hidden_, inter_}}}; }
+  void load(const Loader &l) override {
+    const auto needs = tensor_needs();
+    w_up_ = l.fetch(needs[0]);
+    w_down_ = l.fetch(needs[1]);
+  }
+  std::vector<std::string> kernel_families() const override {
+    std::vector<std::string> fams = product_families(env_.dtype);
+    fams.push_back("moe");
+    return fams;
+  }
+  Act forward(StepContext &ctx, const Act &x) override {
+    Act u = linear(ctx, x, w_up_, nullptr, DType::F32);
+    flush_chain(ctx);
+    Act m = ctx.arena->act(ctx.dtype, x.rows, inter_);
+    kernels::activation(u, m, act_, ctx.stream);
+    return linear(ctx, m, w_down_, nullptr, DType::F32, true);
+  }
+
+ private:
+  int64_t hidden_, inter_;
+  int act_;
+  std::string up_, down_;
+  Weight w_up_, w_down_;
+};
+
+// ---------------------------------------------------------------- routed experts
+// Router logits z = W_router x (a product with 32-bit accumulation and a 32-bit result), scores
+// sigmoid(z) or softmax(z), the `top` largest chosen; their scores, as they are or divided by
+// their sum (`renormalize`), weigh the experts.  `weight_on` "input": the output is the sum of
+// expert(w x); "output": of w expert(x).  Experts are two-matrix feed-forwards whose tensors are
+// named by a pattern with "{}" for the expert's number; they lie stacked on the device,
+// [experts, ff, hidden] and [experts, hidden, ff].  A `shared` feed-forward (any description) runs
+// for every token and is added.  The result is [parts, T, hidden]: a part per choice, then the
+// shared one's, which the stream adds in that order.
+class RoutedFeedForward : public FeedForward {
+ public:
+  RoutedFeedForward(const Json &spec, const BuildEnv &env) : FeedForward(spec, env) {
+    ConfigReader r(spec, "moe description");
+    hidden_ = r.integer("hidden");
+    experts_ = (int)r.integer("experts");
+    top_ = (int)r.integer("top");
+    if (top_ > experts_) r.fail("'top' exceeds 'experts'");
+    const std::string score = r.string_or("score", "softmax");
+    if (score != "sigmoid" && score != "softmax") r.fail("'score' must be \"sigmoid\" or \"softmax\"");
+    score_ = score == "softmax" ? 1 : 0;
+    renormalize_ = r.boolean_or("renormalize", false);
+    const std::string on = r.string_or("weight_on", "output");
+    if (on != "input" && on != "output") r.fail("'weight_on' must be \"input\" or \"output\"");
+    weight_on_output_ = on == "output";
+    router_ = r.string("router");
+    ConfigReader e(r.object("expert"), "moe description: expert");
+    inter_ = e.integer("intermediate");
+    act_ = activation_code(e.string_or("activation", "gelu"), e);
+    up_ = e.string("up");
+    down_ = e.string("down");
+    if (up_.find("{}") == std::string::npos || down_.find("{}") == std::string::npos)
+      e.fail("'up' and 'down' are patterns with \"{}\" for the expert's number");
+    if (r.present("shared")) shared_ = build_as<FeedForward>("feed_forward", r.object("shared"), env);
+  }
+  static std::string numbered(const std::string &pattern, int e) {
+    std::string s = pattern;
+    s.replace(s.find("{}"), 2, std::to_string(e));
+    return s;
+  }
+  std::vector<TensorNeed> tensor_needs() const override {
+    std::vector<TensorNeed> needs = {{router_, {(int64_t)experts_, hidden_}}};
+    for (int e = 0; e < experts_; ++e) {
+      needs.push_back({numbered(up_, e), {inter_, hidden_}});
+      needs.push_back({numbered(down_, e), {hidden_, inter_}});
+    }
+    if (shared_)
+      for (auto &n : shared_->tensor_needs()) needs.push_back(n);
+    return needs;
+  }
+  void load(const Loader &l) override {
+    const auto needs = tensor_needs();
+    w_router_ = l.fetch(needs[0]);
+    const size_t es = dtype_size(l.engine), one = (size_t)(inter_ * hidden_) * es;
+    w_up_.allocate(one * (size_t)experts_);
+    w_down_.allocate(one * (size_t)experts_);
+    for (int e = 0; e < experts_; ++e) {
+      l.fetch_into(needs[1 + 2 * (size_t)e], l.engine, (char *)w_up_.get() + one * (size_t)e);
+      l.fetch_into(needs[2 + 2 * (size_t)e], l.engine, (char *)w_down_.get() + one * (size_t)e);
+    }
+    if (shared_) shared_->load(l);
+  }
+  std::vector<std::string> kernel_families() const override {
+    std::vector<std::string> fams = product_families(env_.dtype);
+    fams.push_back("moe");
+    if (shared_)
+      for (auto &f : shared_->kernel_families()) fams.push_back(f);
+    return fams;
+  }
+  bool capturable() const override { return !shared_ || shared_->capturable(); }
+
+  Act forward(StepContext &ctx, const Act &x) override {
+    const int64_t T = x.rows;
+    // the shared expert first: its last product may add to the residual stream as it stores
+    Act s;
+    if (shared_) s = shared_->forward(ctx, x);
+    const bool s_own = s.data && s.data != (void *)ctx.residual_sink;
+    float *const sink = ctx.residual_sink;
+    ctx.residual_sink = nullptr;                     // what follows returns its own buffers
+    Act z = linear(ctx, x, w_router_, nullptr, DType::F32);
+    ctx.residual_sink = sink;
+    flush_chain(ctx);
+    const int n_rows = (int)T * top_;
+    int *chosen = ctx.arena->alloc_n<int>((size_t)n_rows);
+    float *weight = ctx.arena->alloc_n<float>((size_t)n_rows);
+    kernels::moe_route(z, experts_, top_, score_, renormalize_, chosen, weight, ctx.stream);
+    Act out = ctx.arena->act(DType::F32, T, hidden_, top_ + (s_own ? s.parts : 0));
+    if (x.dtype == DType::BF16 && kernels::moe_grouped_supported((int)hidden_, (int)inter_) && x.ld % 8 == 0 &&
+        (uintptr_t)x.data % 16 == 0) {
+      const int tile = kernels::moe_tile_rows();
+      int *offsets = ctx.arena->alloc_n<int>((size_t)experts_ + 1);
+      int *perm = ctx.arena->alloc_n<int>((size_t)n_rows);
+      int *tiles = ctx.arena->alloc_n<int>(1 + 2 * ((size_t)std::min(experts_, n_rows) + (size_t)(n_rows / tile)));
+      void *mid = ctx.arena->alloc((size_t)n_rows * (size_t)inter_ * 2);
+      kernels::moe_sort(chosen, n_rows, experts_, offsets, perm, tiles, ctx.stream);
+      kernels::moe_grouped(x, w_up_.get(), w_down_.get(), offsets, perm, tiles, weight, experts_, top_, (int)hidden_, (int)inter_,
+                           act_, weight_on_output_, mid, (float *)out.data, ctx.stream);
+    } else {
+      kernels::moe_rows(x, w_up_.get(), w_down_.get(), chosen, weight, top_, (int)hidden_, (int)inter_, act_, weight_on_output_,
+                        (float *)out.data, ctx.stream);
+    }
+    if (s_own) {
+      if (s.dtype != DType::F32 || s.rows != T || s.cols != hidden_ || s.ld != hidden_)
+        LLM_THROW(Unsupported, "moe: the shared feed-forward must hand over dense 32-bit rows");
+      for (int p = 0; p < s.parts; ++p)
+        LLM_CUDA(cudaMemcpyAsync((float *)out.data + (size_t)(top_ + p) * (size_t)out.part_stride,
+                                 (const float *)s.data + (size_t)p * (size_t)s.part_stride, sizeof(float) * (size_t)(T * hidden_),
+                                 cudaMemcpyDeviceToDevice, ctx.stream));
+    }
+    return out;
+  }
+
+ private:
+  int64_t hidden_, inter_;
+  int experts_, top_, score_, act_;
+  bool renormalize_, weight_on_output_;
+  std::string router_, up_, down_;
+  Weight w_router_;
+  DeviceBuffer w_up_, w_down_;
+  std::unique_ptr<FeedForward> shared_;
+};
+
+template <typename T>
+PartFactory factory_of() {
+  return [](const Json &spec, const BuildEnv &env) { return std::unique_ptr<Part>(new T(spec, env)); };
+}
+
+}  // namespace
+
+void register_part_raw(const std::string &category, const std::string &kind, PartFactory factory);   // parts/part.cc
+
+void register_feed_forward_parts() {
+  register_part_raw("feed_forward", "mlp", factory_of<Mlp>());
+  register_part_raw("feed_forward", "moe", factory_of<RoutedFeedForward>());
+}
+
+}  // namespace llm

@@ -45,7 +45,8 @@ struct BuildEnv {
 };
 
 // Keys and values a mixer wants kept per sequence.  kind "full" keeps every position, "window"
-// only the last `window` (older pages are given back).  Keys and values have widths of their
+// only the last `window` (older pages are given back), "block" only the positions of the block of
+// `block` positions (counted from 0) that the next token falls into.  Keys and values have widths of their
 // own; v_dim 0 keeps one vector per position (a latent) in the key storage alone.
 struct CacheNeed {
   std::string kind = "full";
@@ -53,8 +54,10 @@ struct CacheNeed {
   int k_dim = 0;
   int v_dim = 0;
   int window = 0;                    // 0: none
+  int block = 0;                     // 0: none
   bool operator==(const CacheNeed &o) const {
-    return kind == o.kind && n_kv_heads == o.n_kv_heads && k_dim == o.k_dim && v_dim == o.v_dim && window == o.window;
+    return kind == o.kind && n_kv_heads == o.n_kv_heads && k_dim == o.k_dim && v_dim == o.v_dim && window == o.window &&
+           block == o.block;
   }
 };
 

@@ -18,6 +18,7 @@ Json ModelSpec::to_json() const {
     Json o = Json::object();
     o.set("layer", e.layer);
     o.set("cache_from", e.cache_from < 0 ? Json() : Json(e.cache_from));
+    o.set("input_mix", e.input_mix.empty() ? Json() : Json(e.input_mix));
     sch.push(o);
   }
   j.set("schedule", sch);
@@ -59,6 +60,7 @@ ModelSpec ModelSpec::from_json(const Json &j) {
         ConfigReader er(e, "model description: schedule entry");
         se.layer = (int)er.integer("layer", 0);
         se.cache_from = (int)er.integer_or("cache_from", -1, 0);
+        se.input_mix = er.string_or("input_mix", "");
       } else {
         r.fail("a schedule entry is a layer number or {layer, cache_from}");
       }

@@ -15,7 +15,11 @@
 //                          position (a position description or null), window (null: all keys),
 //                          scale (null: 1/sqrt(head_dim)), bias, q, k, v, o (tensor names)
 //   feed_forward "swiglu": hidden, intermediate, gate, up, down (tensor names)
+//   mixer "attention" also: v_head_dim, qk_norm {q, k, eps}, block (mask), head_gate (parts/builtin.cc)
+//   feed_forward "mlp":    hidden, intermediate, activation (gelu, gelu_tanh, silu), up, down
+//   feed_forward "moe":    hidden, experts, top, score, renormalize, weight_on, router, expert {..}, shared
 //   block "prenorm":       mixer_norm, mixer, ff_norm, ff (descriptions)
+//   block "parallel":      norm, mixer, ff (a description or null): x + mixer(norm x) + ff(norm x)
 #pragma once
 #include <string>
 #include <vector>
@@ -27,9 +31,13 @@ namespace llm {
 // One run of a layer.  `layer` indexes ModelSpec::layers; the same layer may be named by several
 // entries (its weights are then used twice, each run with a cache of its own).  `cache_from`
 // names an earlier entry whose cache this run reads instead of keeping one: it appends nothing.
+// `input_mix` names a matrix [hidden, 2 * hidden]: right before this run the residual stream x
+// becomes W [x; x0], x0 being the token rows as they entered the first layer (a model that runs some
+// of its layers several times feeds the tokens to every pass this way).
 struct ScheduleEntry {
   int layer = 0;
   int cache_from = -1;
+  std::string input_mix;
 };
 
 struct ModelSpec {

@@ -228,8 +228,8 @@ def test_prenorm_block_alone(dtype):
 
 def test_a_part_refuses_what_it_cannot_do():
     from libllm_b200.errors import ConfigError, UnsupportedError, WeightsError
-    with pytest.raises(UnsupportedError, match="head size 24"):
-        part("mixer", attention_spec(48, 2, 1, 24, None), "bfloat16")
+    with pytest.raises(UnsupportedError, match="head sizes 264"):
+        part("mixer", attention_spec(48, 2, 1, 264, None), "bfloat16")
     with pytest.raises(ConfigError, match="not a multiple"):
         part("mixer", attention_spec(48, 3, 2, 16, None), "bfloat16")
     with pytest.raises(ConfigError, match="no feed_forward of kind 'gelu_mlp'.*swiglu"):

@@ -23,7 +23,7 @@ def library():
     build.ensure_built(["attention_decode"])
     lib = ctypes.CDLL(build.library_path("attention_decode"))
     common = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_float]
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float]
     lib.llm_attention_decode.argtypes = common + [c_void_p, c_void_p, c_void_p]
     lib.llm_attention_decode_static.argtypes = common + [c_void_p]
     lib.llm_attention_decode.restype = lib.llm_attention_decode_static.restype = c_int
@@ -58,7 +58,7 @@ def call(lib, static, q, K, V, table, pos, n_heads, n_kv, d, chunk, n_splits):
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
     args = [c_void_p(q.data_ptr()), q.stride(0), c_void_p(out.data_ptr()), out.stride(0), c_void_p(K.data_ptr()),
             c_void_p(V.data_ptr()), c_void_p(pos.data_ptr()), c_void_p(table.data_ptr()), table.stride(0), B, n_heads,
-            n_kv, d, 64, chunk, n_splits, 0, c_float(1.0 / math.sqrt(d))]
+            n_kv, d, 64, chunk, n_splits, 0, 0, c_float(1.0 / math.sqrt(d))]
     if static:
         rc = lib.llm_attention_decode_static(*args, stream)
     else:
