@@ -13,7 +13,7 @@ from .. import _lib
 
 class CacheBook:
     """The books of a cache: ``runs[i]`` is what schedule entry i wants cached (None: nothing of
-    its own; else {"kind", "n_kv_heads", "k_dim", "v_dim", "window"}), ``states[i]`` its fixed-size
+    its own; else {"kind", "n_kv_heads", "k_dim", "v_dim", "window", "block"}), ``states[i]`` its fixed-size
     state tensors [{"name", "shape"}]."""
 
     def __init__(self, runs: Sequence[Optional[Dict[str, Any]]], states: Sequence[Sequence[Dict[str, Any]]] = (),

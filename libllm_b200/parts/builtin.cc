@@ -196,8 +196,8 @@ class Attention : public Mixer {
     gate_offset_ = q_width_ + kv_width_ + v_width_;
     // rows of the stacked matrix: a multiple of 8, so that rows of the 32-bit product start on 32 bytes
     stacked_rows_ = (gate_offset_ + (gate_name_.empty() ? 0 : n_heads_) + 7) / 8 * 8;
-    // what the kernels written for the reference's attention do not take (they get the general ones)
-    plain_ = dv_ == d_ && q_norm_name_.empty() && d_ % 16 == 0 && d_ >= 16;
+    // the tiled attention kernels take heads whose values are as wide as their keys, in multiples of 16
+    plain_ = dv_ == d_ && d_ % 16 == 0 && d_ >= 16;
   }
 
   std::vector<TensorNeed> tensor_needs() const override {
@@ -272,7 +272,7 @@ class Attention : public Mixer {
     const bool tiled = env_.page_size == 64 && d_ % 16 == 0 && d_ >= 16 && d_ <= 128;
     if (f.prefill_attention_tc && env_.page_size == 64 && (d_ == 64 || d_ == 128)) fams.push_back("attention_prefill_tc");
     else if (f.prefill_attention && tiled) fams.push_back("attention_prefill");
-    if (f.decode_attention_tc && tiled && group <= 16 && !bias_ && position_ && gate_name_.empty())
+    if (f.decode_attention_tc && tiled && group <= 16 && !bias_ && position_ && gate_name_.empty() && q_norm_name_.empty())
       fams.push_back("attention_decode_tc");
     else if (f.decode_attention && (d_ == 16 || d_ == 32 || d_ == 64 || d_ == 128) &&
              (group == 1 || group == 2 || group == 3 || group == 4 || group == 8))
@@ -303,7 +303,7 @@ class Attention : public Mixer {
     const float *table = position_ ? position_->half_split_table(&table_rows, &rot_dim) : nullptr;
     const bool has_gate = !gate_name_.empty();
     const float *gate = nullptr;
-    const bool fused = plain_ && !has_gate && table && !bias_ && ctx.decode_only && f.decode_attention_tc && ctx.dtype == DType::BF16 &&
+    const bool fused = plain_ && !has_gate && q_norm_name_.empty() && table && !bias_ && ctx.decode_only && f.decode_attention_tc && ctx.dtype == DType::BF16 &&
                        kernels::available("attention_decode_tc") && kernels::attention_decode_tc_supported(d_, cache->page_size, group);
     Act qkv = linear(ctx, x, w_qkv_, bias_ ? b_qkv_.buf.as<float>() : nullptr, DType::F32, fused);
     flush_chain(ctx);

@@ -47,9 +47,27 @@ def chunk_mask(q_pos: torch.Tensor, k_pos: torch.Tensor, size: int) -> torch.Ten
     return (kj <= qi) & (torch.div(qi, size, rounding_mode="floor") == torch.div(kj, size, rounding_mode="floor"))
 
 
+def attention_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos: torch.Tensor, k_pos: torch.Tensor, scale: float,
+                   block: Optional[int], gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [Tq, H, d], k [Tk, G, d], v [Tk, G, dv] -> [Tq, H, dv]: softmax over the visible keys of
+    scale * q.k, head h reading kv head h // (H / G); ``gate`` [Tq, H] multiplies by its sigmoid."""
+    H, G = q.shape[1], k.shape[1]
+    visible = chunk_mask(q_pos, k_pos, block if block else 1 << 40)
+    out = torch.zeros(q.shape[0], H, v.shape[2], dtype=F)
+    for head in range(H):
+        g = head // (H // G)
+        s = (q[:, head].to(F) @ k[:, g].to(F).T) * scale
+        a = torch.softmax(s.masked_fill(~visible, -math.inf), dim=-1)
+        out[:, head] = a @ v[:, g].to(F)
+        if gate is not None:
+            out[:, head] *= torch.sigmoid(gate[:, head:head + 1].to(F))
+    return out
+
+
 def attention_mixer(m: dict, w: Dict[str, torch.Tensor], p: str, h: torch.Tensor, pos: torch.Tensor, eps: float) -> torch.Tensor:
     """The attention mixer on the normalised input h [T, width] of positions pos [T]."""
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, G, d = m["heads"], m.get("kv_heads", m["heads"]), m["dim"]
+    dv = m.get("vdim", d)
     T = h.shape[0]
     q = h @ w[p + "mix.q"].T
     k = h @ w[p + "mix.k"].T
@@ -57,18 +75,13 @@ def attention_mixer(m: dict, w: Dict[str, torch.Tensor], p: str, h: torch.Tensor
     # one norm over the whole projection, before the heads are split and before the rotation
     q = rms_norm(q, w[p + "mix.q.norm"], eps)
     k = rms_norm(k, w[p + "mix.k.norm"], eps)
-    q = rotate(q.reshape(T, H, d), pos, m["rot"]["dims"], m["rot"]["base"])
-    k = rotate(k.reshape(T, G, d), pos, m["rot"]["dims"], m["rot"]["base"])
+    q, k = q.reshape(T, H, d), k.reshape(T, G, d)
+    if m.get("rot"):
+        q = rotate(q, pos, m["rot"]["dims"], m["rot"]["base"])
+        k = rotate(k, pos, m["rot"]["dims"], m["rot"]["base"])
     v = v.reshape(T, G, dv)
-    visible = chunk_mask(pos, pos, m["mask"]["size"])
-    gate = torch.sigmoid(h @ w[p + "mix.g"].T)                              # [T, H]
-    out = torch.zeros(T, H, dv, dtype=F)
-    for head in range(H):
-        g = head // (H // G)
-        s = (q[:, head] @ k[:, g].T) * m["scale"]
-        s = s.masked_fill(~visible, -math.inf)
-        a = torch.softmax(s, dim=-1)
-        out[:, head] = (a @ v[:, g]) * gate[:, head:head + 1]
+    # without a mask entry every earlier key is visible
+    out = attention_core(q, k, v, pos, pos, m["scale"], m["mask"]["size"] if m.get("mask") else None, h @ w[p + "mix.g"].T)
     return out.reshape(T, H * dv) @ w[p + "mix.o"].T
 
 

@@ -95,7 +95,7 @@ def test_an_architecture_registered_from_outside_is_described_by_its_own_functio
     assert "test_two_runs" in known_architectures()
     d = describe_model(dict(model_type="test_two_runs", width=32))
     assert [n["name"] for n in d["tensor_needs"]] == ["emb", "l.n1", "l.q", "l.k", "l.v", "l.o", "l.n2", "l.g", "l.u", "l.d", "fn"]
-    assert d["spec"]["schedule"] == [dict(layer=0, cache_from=None), dict(layer=0, cache_from=0)]
+    assert d["spec"]["schedule"] == [dict(layer=0, cache_from=None, input_mix=None), dict(layer=0, cache_from=0, input_mix=None)]
     with pytest.raises(ConfigError, match="KeyError.*width"):
         describe_model(dict(model_type="test_two_runs"))
     bad = lambda c: dict(describe(c), schedule=[dict(layer=0, cache_from=0)])
