@@ -303,6 +303,105 @@ def run_workload(args):
     return 0
 
 
+# ---------------------------------------------------------------- Sinezen beside Llama at equal sizes
+def sinezen_config(hidden, runs, heads, kv, dim, ff, vocab, mask, moe=None):
+    """A Sinezen model of `runs` layer runs: two layers before a loop of two layers that repeats as
+    often as the runs ask for.  `moe` = (experts, top, expert ff, shared ff) puts a routed feed-forward
+    into every second layer."""
+    mixer = dict(heads=heads, kv_heads=kv, dim=dim, vdim=dim, scale=dim ** -0.5, mask=dict(size=mask),
+                 rot=dict(base=500000.0, dims=dim))
+    dense = dict(kind="dense", ff=ff)
+    routed = dense if moe is None else dict(kind="moe", router=dict(experts=moe[0], top=moe[1]), expert=dict(ff=moe[2]),
+                                            shared=dict(ff=moe[3]))
+    layer = lambda mlp: dict(type="attention", mixer=mixer, mlp=mlp)
+    times = max(1, (runs - 2) // 2)
+    return dict(architecture="Sinezen", vocab=vocab, width=hidden, norm=dict(eps=1e-5),
+                layers=[layer(dense), layer(routed), layer(dense), layer(routed)], loop=dict(start=2, stop=4, times=times))
+
+
+def sinezen_numbers(c, batch):
+    """(bytes a decode step reads at `batch` apart from the cache, cache bytes per visible token,
+    prefill flops of T tokens with one wanted row) for a Sinezen configuration."""
+    H, V = c["width"], c["vocab"]
+    loop = c["loop"]
+    runs = list(range(loop["start"])) + list(range(loop["start"], loop["stop"])) * loop["times"] + \
+        list(range(loop["stop"], len(c["layers"])))
+
+    def layer_mats(L, tokens):
+        """(matrix values every token uses, matrix values the step reads) of one layer"""
+        m, f = L["mixer"], L["mlp"]
+        att = H * (m["heads"] * m["dim"] + m["kv_heads"] * (m["dim"] + m["vdim"]) + m["heads"]) + m["heads"] * m["vdim"] * H
+        if f["kind"] == "dense":
+            return att + 3 * H * f["ff"], att + 3 * H * f["ff"]
+        E, top, eff, sff = f["router"]["experts"], f["router"]["top"], f["expert"]["ff"], f["shared"]["ff"]
+        used = att + H * E + 2 * H * (top * eff + sff)
+        return used, att + H * E + 2 * H * (min(E, tokens * top) * eff + sff)
+
+    # a layer that runs twice is read twice: the runs between its two uses read more than L2 holds
+    weight_bytes = 2 * (sum(layer_mats(c["layers"][i], batch)[1] for i in runs) + 2 * V * H + loop["times"] * 2 * H * H)
+    kv_per_token = sum(2 * c["layers"][i]["mixer"]["kv_heads"] * (c["layers"][i]["mixer"]["dim"] + c["layers"][i]["mixer"]["vdim"]) for i in runs)
+
+    def prefill_flops(T):
+        lin = 2 * T * sum(layer_mats(c["layers"][i], T)[0] for i in runs) + loop["times"] * 2 * T * 2 * H * H
+        att = 0
+        for i in runs:
+            m = c["layers"][i]["mixer"]
+            B = m["mask"]["size"]
+            full, rest = divmod(T, B)
+            seen = full * B * (B + 1) // 2 + rest * (rest + 1) // 2
+            att += 2 * m["heads"] * (m["dim"] + m["vdim"]) * seen
+        return lin + att + 2 * V * H
+    return weight_bytes, kv_per_token, prefill_flops
+
+
+COMPARE_SIZES = {
+    # name: (hidden, layer runs, heads, kv heads, head size, feed-forward, vocabulary, mask, routed)
+    "2k": (2048, 8, 32, 8, 64, 8192, 32000, 1024, None),
+    "4k": (4096, 4, 32, 8, 128, 14336, 32000, 2048, None),
+    "2k-routed": (2048, 8, 32, 8, 64, 4096, 32000, 1024, (32, 4, 1024, 2048)),
+}
+
+
+def run_compare(args):
+    """Prefill and decode of Sinezen beside Llama, both with random weights, at equal hidden size, layer
+    runs, heads, head size, feed-forward width (with experts: equal matrix values used per token) and
+    vocabulary: one JSON line per size and model."""
+    import torch
+    from libllm_b200 import Model
+    pk = peaks()
+    names = [n for n in COMPARE_SIZES if not args.sizes or n in args.sizes.split(",")]
+    for name in names:
+        hidden, runs, heads, kv, dim, ff, vocab, mask, routed = COMPARE_SIZES[name]
+        llama = dict(LLAMA_1B, num_hidden_layers=runs, hidden_size=hidden, num_attention_heads=heads, num_key_value_heads=kv,
+                     head_dim=dim, intermediate_size=ff, vocab_size=vocab, tie_word_embeddings=False, rope_scaling=None)
+        zen = sinezen_config(hidden, runs, heads, kv, dim, ff, vocab, mask, routed)
+        for label, cfg in (("llama", llama), ("sinezen", zen)):
+            if label == "llama":
+                wbytes, kv_per_tok, flops_fn = model_numbers(cfg)
+                flops = flops_fn(PROMPT)
+            else:
+                wbytes, kv_per_tok, zen_flops = sinezen_numbers(cfg, args.batch)
+                flops = zen_flops(PROMPT)
+            model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=args.batch * CONTEXT, max_seq_len=CONTEXT)
+            pre = prefill_rate(model, vocab, lambda T: flops, pk["bf16_tflops"])
+            rate, ms, ctx_len, launches = decode_rate(model, args.batch, args.steps, args.warmup, vocab)
+            seen = ctx_len if label == "llama" else min(ctx_len, ctx_len % mask + 1)
+            step_bytes = wbytes + args.batch * seen * kv_per_tok
+            print(json.dumps({"compare": name, "model": label, "batch": args.batch, "prompt": PROMPT,
+                              "config": {"hidden": hidden, "layer_runs": runs, "heads": heads, "kv_heads": kv, "head_dim": dim, "ff": ff,
+                                         "vocab": vocab, "mask": mask if label == "sinezen" else None, "routed": routed if label == "sinezen" else None},
+                              "prefill": {"ms": round(pre["ms"], 3), "tok_s": round(pre["value"], 1), "tflop": round(flops / 1e12, 3),
+                                          "frac_of_gemm_peak": round(pre["frac"], 4)},
+                              "decode": {"tok_s": round(rate, 1), "ms_per_step": round(ms, 4), "launches_per_step": launches,
+                                         "step_gb": round(step_bytes / 1e9, 3),
+                                         "hbm_frac": round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)},
+                              "peaks": pk["source"]}), flush=True)
+            model.engine.close()
+            del model
+            torch.cuda.empty_cache()
+    return 0
+
+
 def run_reference(args):
     """The reference arm: ling0322/libllm's unmodified C++/CUDA code (compiled into baseline/_ref by
     baseline/reference_arm.py; it has no installable Python package of its engine) at the same layer
@@ -377,11 +476,14 @@ def main():
                     help="1b: the benchmark line (default); 3b, 8b: the larger workloads, a line of their own")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print a short line (for profiling; not a bench record)")
+    ap.add_argument("--compare", choices=["sinezen"], default=None,
+                    help="Sinezen beside Llama at equal sizes: prefill and decode, a line per size and model (not a bench record)")
+    ap.add_argument("--sizes", default=None, help="with --compare: which of the sizes (2k, 4k, 2k-routed), with commas")
     ap.add_argument("--prompt-len", type=int, default=None,
                     help="with --only: prompts of this many tokens instead of 2048 (the context grows to fit)")
     args = ap.parse_args()
     if args.prompt_len:
-        if not args.only:
+        if not args.only and not args.compare:
             print("bench.py: --prompt-len goes with --only (the record is taken at the sizes BASELINE.json names)")
             return 2
         global PROMPT, CONTEXT
@@ -393,6 +495,8 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.compare:
+        return run_compare(args)
     if args.workload != "1b":
         return run_workload(args)
 

@@ -208,7 +208,7 @@ static int launch_add_rmsnorm(float *resid, const void *delta, int n_parts, size
   constexpr int VPT = 4;
   const bool aligned = hidden % 4 == 0 && (uintptr_t)resid % 16 == 0 && (uintptr_t)delta % 16 == 0 &&
                        (uintptr_t)weight % 16 == 0 && (uintptr_t)out % 16 == 0 && part_stride % 4 == 0;
-  if (aligned && hidden <= 4 * VPT * THREADS && n_parts <= 8) {
+  if (aligned && hidden <= 4 * VPT * THREADS && n_parts <= 16) {
     // one instantiation per bound on the parts: registers for eight parts cost a prompt step
     // (one part, thousands of rows) a third of its speed
     // A thread per four columns where the row allows it (up to 4,096 columns): with many parts the
@@ -224,7 +224,8 @@ static int launch_add_rmsnorm(float *resid, const void *delta, int n_parts, size
   } while (0)
     if (n_parts <= 1) ADDNORM_GO(1);
     else if (n_parts <= 4) ADDNORM_GO(4);
-    else ADDNORM_GO(8);
+    else if (n_parts <= 8) ADDNORM_GO(8);
+    else ADDNORM_GO(16);                   // a mixer's and a feed-forward's parts together (a parallel block)
 #undef ADDNORM_GO
 #undef ADDNORM_GO2
     LLM_CHECK_LAUNCH("add_rmsnorm");
@@ -489,10 +490,41 @@ __global__ void head_gate_kernel(T *__restrict__ x, long long ld, const float *_
   }
 }
 
+// Four channels to a thread (head widths that are a multiple of 4, 8-byte aligned rows).
+template <typename T>
+__global__ void head_gate_vec_kernel(T *__restrict__ x, long long ld, const float *__restrict__ gate, long long gate_stride,
+                                     int n_heads, int dv4, size_t total4) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  const int width4 = n_heads * dv4;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / width4;
+    const int c4 = (int)(idx - t * width4);
+    const float g = 1.f / (1.f + expf(-gate[t * gate_stride + c4 / dv4]));
+    T *p = x + t * ld + 4 * c4;
+    const float4 v = ld4(p);
+    st4(p, make_float4(v.x * g, v.y * g, v.z * g, v.w * g));
+  }
+}
+
 LLM_EXPORT int llm_head_gate(void *x, int dtype, long long ld, const float *gate, long long gate_stride, int n_tokens,
                              int n_heads, int dv, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && dv > 0 && x && gate, "head_gate: bad arguments");
+  if (dv % 4 == 0 && ld % 4 == 0 && (uintptr_t)x % 16 == 0) {
+    const size_t total4 = (size_t)n_tokens * n_heads * (dv / 4);
+    size_t blocks4 = (total4 + 255) / 256;
+    if (blocks4 > (size_t)sm_count() * 32) blocks4 = (size_t)sm_count() * 32;
+    if (dtype == LLM_F32)
+      llm_launch(head_gate_vec_kernel<float>, dim3((unsigned)blocks4), dim3(256), 0, stream, (float *)x, ld, gate, gate_stride,
+                 n_heads, dv / 4, total4);
+    else if (dtype == LLM_BF16)
+      llm_launch(head_gate_vec_kernel<__nv_bfloat16>, dim3((unsigned)blocks4), dim3(256), 0, stream, (__nv_bfloat16 *)x, ld, gate,
+                 gate_stride, n_heads, dv / 4, total4);
+    else LLM_FAIL("head_gate: unknown dtype %d", dtype);
+    LLM_CHECK_LAUNCH("head_gate");
+    return LLM_OK;
+  }
   const size_t total = (size_t)n_tokens * n_heads * dv;
   size_t blocks = (total + 255) / 256;
   if (blocks > (size_t)sm_count() * 32) blocks = (size_t)sm_count() * 32;

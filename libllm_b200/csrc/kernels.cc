@@ -278,8 +278,9 @@ void qk_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, in
 LLM_KERNEL("attention_generic", llm_attention_generic, int, const void *, long long, void *, long long, const void *, const void *,
            const int *, const int *, const int *, int, int, int, int, int, int, int, int, int, float, const float *, long long,
            cudaStream_t)
-LLM_KERNEL("attention_decode", llm_attention_decode, const void *, long long, void *, long long, const void *, const void *,
-           const int *, const int *, int, int, int, int, int, int, int, int, int, int, float, float *, float *, cudaStream_t)
+LLM_KERNEL("attention_decode", llm_attention_decode_gated, const void *, long long, void *, long long, const void *, const void *,
+           const int *, const int *, int, int, int, int, int, int, int, int, int, int, float, float *, float *, const float *,
+           long long, cudaStream_t)
 LLM_KERNEL("attention_decode_tc", llm_attention_decode_tc, const float *, long long, int, long long, const float *, int, int,
            const int *, const int *, int, void *, void *, int, int, int, int, int, int, int, int, int, int, int, float, float *,
            float *, int *, void *, long long, cudaStream_t)
@@ -306,11 +307,12 @@ bool attention_decode_supported(int d, int group) {
 }
 void attention_decode(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                       int pt_stride, int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window,
-                      int block, float scale, float *ws_o, float *ws_ml, cudaStream_t s) {
+                      int block, float scale, float *ws_o, float *ws_ml, const float *gate, long long gate_stride,
+                      cudaStream_t s) {
   const int B = (int)q.rows;
-  LLM_CALL("attention_decode", llm_attention_decode, q.data, (long long)(B > 1 ? q.ld : q.cols), out.data,
+  LLM_CALL("attention_decode", llm_attention_decode_gated, q.data, (long long)(B > 1 ? q.ld : q.cols), out.data,
            (long long)(B > 1 ? out.ld : out.cols), kc, vc, tok_pos, page_table, pt_stride, B, n_heads, n_kv, d, page_size, chunk,
-           n_splits, window, block, scale, ws_o, ws_ml, s);
+           n_splits, window, block, scale, ws_o, ws_ml, gate, gate_stride, s);
 }
 bool attention_decode_tc_supported(int d, int page_size, int group) {
   static auto f = resolve<int (*)(int, int, int)>("attention_decode_tc", "llm_attention_decode_tc_supports");

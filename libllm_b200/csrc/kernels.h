@@ -93,7 +93,8 @@ void attention_generic(const Act &q, const Act &out, const void *kc, const void 
 bool attention_decode_supported(int d, int group);
 void attention_decode(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                       int pt_stride, int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window,
-                      int block, float scale, float *ws_o, float *ws_ml, cudaStream_t s);
+                      int block, float scale, float *ws_o, float *ws_ml, const float *gate, long long gate_stride,
+                      cudaStream_t s);
 bool attention_decode_tc_supported(int d, int page_size, int group);
 int attention_decode_tc_ctas_per_sm(int d);
 void attention_decode_tc(const Act &qkv, const float *table, int table_rows, int rot_dim, const int *tok_pos,

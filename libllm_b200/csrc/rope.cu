@@ -237,6 +237,113 @@ qk_place_kernel(const TI *__restrict__ qkv, long long row_stride, T *__restrict_
   }
 }
 
+// The same four channels (or channel pairs) to a thread, for widths that are multiples of 4 (the
+// rotated width of 8) and 16-byte aligned rows: both sums of squares go through one reduction.
+template <typename TI, typename T>
+__global__ void __launch_bounds__(256)
+qk_place_vec_kernel(const TI *__restrict__ qkv, long long row_stride, T *__restrict__ q_out, long long q_stride,
+                    int n_heads, int n_kv, int d, int dv, const float *__restrict__ q_norm,
+                    const float *__restrict__ k_norm, float eps, const float *__restrict__ table, int table_rows,
+                    int rot_dim, const int *__restrict__ tok_seq, const int *__restrict__ tok_pos,
+                    const int *__restrict__ page_table, int pt_stride, T *__restrict__ kcache,
+                    T *__restrict__ vcache, int page_size, int write_cache) {
+  __shared__ float sq[256 / 32 + 1], sk[256 / 32 + 1];
+  grid_dependents_launch();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  const TI *row = qkv + (size_t)t * row_stride;
+  const int qw = n_heads * d, kw = n_kv * d;
+  float q_fac = 1.f, k_fac = 1.f;
+  if (q_norm) {
+    float ssq = 0.f, ssk = 0.f;
+    for (int c = threadIdx.x * 4; c < qw; c += 1024) {
+      const float4 v = ld4(row + c);
+      ssq = fmaf(v.x, v.x, ssq);
+      ssq = fmaf(v.y, v.y, ssq);
+      ssq = fmaf(v.z, v.z, ssq);
+      ssq = fmaf(v.w, v.w, ssq);
+    }
+    if (write_cache)
+      for (int c = threadIdx.x * 4; c < kw; c += 1024) {
+        const float4 v = ld4(row + qw + c);
+        ssk = fmaf(v.x, v.x, ssk);
+        ssk = fmaf(v.y, v.y, ssk);
+        ssk = fmaf(v.z, v.z, ssk);
+        ssk = fmaf(v.w, v.w, ssk);
+      }
+    // warps first, then the warp totals in warp order (a fixed order of additions)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    ssq = warp_sum(ssq);
+    ssk = warp_sum(ssk);
+    if (lane == 0) {
+      sq[warp] = ssq;
+      sk[warp] = ssk;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      float a = lane < 8 ? sq[lane] : 0.f, b = lane < 8 ? sk[lane] : 0.f;
+      a = warp_sum(a);
+      b = warp_sum(b);
+      if (lane == 0) {
+        sq[8] = a;
+        sk[8] = b;
+      }
+    }
+    __syncthreads();
+    q_fac = 1.f / sqrtf(sq[8] / (float)qw + eps);
+    k_fac = 1.f / sqrtf(sk[8] / (float)kw + eps);
+  }
+  size_t cache_row = 0;
+  if (write_cache) {
+    const int page = page_table[(size_t)tok_seq[t] * pt_stride + pos / page_size];
+    cache_row = (size_t)page * n_kv * page_size + (pos % page_size);
+  }
+  const int half = rot_dim / 2;
+  const float *cs = table ? table + (size_t)(pos < table_rows ? pos : table_rows - 1) * rot_dim : nullptr;
+  const int per_head = (d - half) / 4;          // groups of four: `half / 4` of pairs, then channels that are not rotated
+  const int n_rot = (n_heads + (write_cache ? n_kv : 0)) * per_head;
+  for (int item = threadIdx.x; item < n_rot; item += 256) {
+    const int slot = item / per_head, i = (item - slot * per_head) * 4;
+    const bool is_q = slot < n_heads;
+    const TI *src = row + (size_t)slot * d;
+    const float *nw = is_q ? (q_norm ? q_norm + (size_t)slot * d : nullptr) : (k_norm ? k_norm + (size_t)(slot - n_heads) * d : nullptr);
+    const float fac = is_q ? q_fac : k_fac;
+    T *dst = is_q ? q_out + (size_t)t * q_stride + (size_t)slot * d
+                  : kcache + (cache_row + (size_t)(slot - n_heads) * page_size) * d;
+    if (i < half) {
+      float4 a = ld4(src + i), b = ld4(src + i + half);
+      a = make_float4(a.x * fac, a.y * fac, a.z * fac, a.w * fac);
+      b = make_float4(b.x * fac, b.y * fac, b.z * fac, b.w * fac);
+      if (nw) {
+        const float4 wa = ld4(nw + i), wb = ld4(nw + i + half);
+        a = make_float4(a.x * wa.x, a.y * wa.y, a.z * wa.z, a.w * wa.w);
+        b = make_float4(b.x * wb.x, b.y * wb.y, b.z * wb.z, b.w * wb.w);
+      }
+      const float4 c = ld4(cs + i), s = ld4(cs + half + i);
+      st4(dst + i, make_float4(a.x * c.x - b.x * s.x, a.y * c.y - b.y * s.y, a.z * c.z - b.z * s.z, a.w * c.w - b.w * s.w));
+      st4(dst + i + half, make_float4(b.x * c.x + a.x * s.x, b.y * c.y + a.y * s.y, b.z * c.z + a.z * s.z, b.w * c.w + a.w * s.w));
+    } else {
+      const int ch = i + half;
+      float4 a = ld4(src + ch);
+      a = make_float4(a.x * fac, a.y * fac, a.z * fac, a.w * fac);
+      if (nw) {
+        const float4 wa = ld4(nw + ch);
+        a = make_float4(a.x * wa.x, a.y * wa.y, a.z * wa.z, a.w * wa.w);
+      }
+      st4(dst + ch, a);
+    }
+  }
+  if (write_cache) {
+    const TI *vsrc = row + qw + kw;
+    const int dv4 = dv / 4;
+    for (int item = threadIdx.x; item < n_kv * dv4; item += 256) {
+      const int kvh = item / dv4, ch = (item - kvh * dv4) * 4;
+      st4(vcache + (cache_row + (size_t)kvh * page_size) * dv + ch, ld4(vsrc + (size_t)kvh * dv + ch));
+    }
+  }
+}
+
 LLM_EXPORT int llm_qk_place(int in_dtype, int dtype, const void *qkv, long long row_stride, void *q_out,
                             long long q_stride, int n_tokens, int n_heads, int n_kv, int d, int dv,
                             const float *q_norm, const float *k_norm, float eps, const float *table,
@@ -248,8 +355,13 @@ LLM_EXPORT int llm_qk_place(int in_dtype, int dtype, const void *qkv, long long 
   LLM_REQUIRE(rot_dim % 2 == 0 && rot_dim <= d && rot_dim >= 0 && (rot_dim == 0 || table != nullptr),
               "qk_place: rotated width %d does not fit head size %d", rot_dim, d);
   LLM_REQUIRE(row_stride >= (long long)n_heads * d + (long long)n_kv * (d + dv), "qk_place: the stacked rows are too short");
+  LLM_REQUIRE((q_norm == nullptr) == (k_norm == nullptr), "qk_place: the norm has weights for both q and k or for neither");
+  const bool vec = d % 4 == 0 && dv % 4 == 0 && rot_dim % 8 == 0 && row_stride % 4 == 0 && q_stride % 4 == 0 &&
+                   (uintptr_t)qkv % 16 == 0 && (uintptr_t)q_out % 16 == 0 && (uintptr_t)table % 16 == 0 &&
+                   (uintptr_t)kcache % 16 == 0 && (uintptr_t)vcache % 16 == 0 && (uintptr_t)q_norm % 16 == 0 &&
+                   (uintptr_t)k_norm % 16 == 0 && ((long long)n_heads * d) % 4 == 0;
 #define QK_PLACE(TI, T)                                                                                          \
-  llm_launch(qk_place_kernel<TI, T>, dim3(n_tokens), dim3(256), 0, stream, (const TI *)qkv, row_stride, (T *)q_out, \
+  llm_launch(vec ? qk_place_vec_kernel<TI, T> : qk_place_kernel<TI, T>, dim3(n_tokens), dim3(256), 0, stream, (const TI *)qkv, row_stride, (T *)q_out, \
              q_stride, n_heads, n_kv, d, dv, q_norm, k_norm, eps, table, table_rows, rot_dim, tok_seq, tok_pos,  \
              page_table, pt_stride, (T *)kcache, (T *)vcache, page_size, write_cache)
   if (in_dtype == LLM_F32 && dtype == LLM_F32) QK_PLACE(float, float);

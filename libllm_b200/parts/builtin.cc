@@ -367,7 +367,9 @@ class Attention : public Mixer {
           ws_ml = ctx.arena->alloc_n<float>((size_t)ctx.n_seqs * n_heads_ * n_splits * 2);
         }
         kernels::attention_decode(q, out, cache->k, cache->v, ctx.tok_pos, cache->page_table, cache->table_width, n_heads_, n_kv_,
-                                  d_, cache->page_size, chunk, n_splits, window_, block_, scale_, ws_o, ws_ml, ctx.stream);
+                                  d_, cache->page_size, chunk, n_splits, window_, block_, scale_, ws_o, ws_ml, gate, qkv.ld,
+                                  ctx.stream);
+        gate = nullptr;                 // applied
         done = true;
       } else if (f.prefill_attention_tc && (d_ == 64 || d_ == 128) && kernels::available("attention_prefill_tc") &&
                  kernels::attention_prefill_tc_supported(d_, cache->page_size)) {
@@ -589,16 +591,49 @@ class ParallelBlock : public Block {
     const bool few = ff_ && ctx.rows_read_after && ctx.n_rows_read_after < stream.rows && !stream.picked;
     Act h_few;
     if (few) h_few = norm_->forward(ctx, stream, ctx.rows_read_after, ctx.n_rows_read_after);
+    // Steps of few tokens, whose products hand back partial products: room in which the mixer's and the
+    // feed-forward's parts lie one behind the other, so that the next norm adds them all in one pass.
+    constexpr int POOL_PARTS = 16;
+    const bool pooled = ff_ && !few && ctx.dtype == DType::BF16 && stream.rows <= fast_switches().tc_tokens && !ctx.chain;
+    if (pooled) {
+      ctx.parts_pool = ctx.arena->alloc_n<float>((size_t)POOL_PARTS * (size_t)(stream.rows * stream.hidden));
+      ctx.parts_cap = POOL_PARTS;
+      ctx.parts_used = 0;
+      ctx.parts_rows = stream.rows;
+      ctx.parts_cols = stream.hidden;
+    }
+    float *const pool = ctx.parts_pool;
     sink(true);
     Act r = mixer_->forward(ctx, h, cache, state);
     sink(false);
     stream.pending = r.data == (void *)stream.resid ? Act() : r;
+    const int mixer_parts = ctx.parts_used;
+    const bool mixer_pooled = pooled && r.data == (void *)pool && r.parts == mixer_parts;
+    if (!mixer_pooled) ctx.parts_pool = nullptr;
     if (ctx.nothing_read_after) {       // no logits wanted from this step: the stream is read by nobody
       flush_chain(ctx);
       stream.pending = Act();
+      ctx.parts_pool = nullptr;
       return;
     }
     if (!ff_) return;
+    if (mixer_pooled) {
+      sink(true);
+      Act f = ff_->forward(ctx, h);
+      sink(false);
+      ctx.parts_pool = nullptr;
+      if (f.data == (void *)(pool + (size_t)mixer_parts * (size_t)r.part_stride) && f.parts == ctx.parts_used - mixer_parts) {
+        r.parts = ctx.parts_used;             // the mixer's parts, then the feed-forward's
+        stream.pending = r;
+        return;
+      }
+      // the feed-forward put its result elsewhere: the mixer's parts are added first, then its own stay pending
+      flush_chain(ctx);
+      kernels::add_rmsnorm(stream.resid, &stream.pending, nullptr, 0.f, nullptr, ctx.dtype, nullptr, (int)stream.rows,
+                           (int)stream.hidden, ctx.stream);
+      stream.pending = f.data == (void *)stream.resid ? Act() : f;
+      return;
+    }
     if (few) {
       flush_chain(ctx);
       const int64_t n = ctx.n_rows_read_after;

@@ -137,7 +137,20 @@ Act small_batch_linear(StepContext &ctx, const Act &x, const Weight &w, DType ou
   if (f.gemm_tc && T <= f.tc_tokens && !use_gemv && kernels::gemm_tc_supported(x, w)) {
     int parts = 1;
     if (parts_ok && !swiglu && out_dtype == DType::F32) parts = kernels::gemm_tc_suggest_parts(T, n, K);
-    Act out = ctx.arena->act(out_dtype, T, n, parts > 1 ? parts : 1);
+    Act out;
+    if (parts_ok && !swiglu && out_dtype == DType::F32 && ctx.parts_pool && ctx.parts_rows == T && ctx.parts_cols == n &&
+        ctx.parts_used + parts <= ctx.parts_cap) {
+      // the block's room for results that are added together (StepContext::parts_pool)
+      out.dtype = DType::F32;
+      out.rows = T;
+      out.cols = out.ld = n;
+      out.parts = parts;
+      out.part_stride = (int64_t)T * n;
+      out.data = ctx.parts_pool + (size_t)ctx.parts_used * (size_t)out.part_stride;
+      ctx.parts_used += parts;
+    } else {
+      out = ctx.arena->act(out_dtype, T, n, parts > 1 ? parts : 1);
+    }
     if (ctx.chain && ctx.chain->add_product(x, w, out, swiglu, ctx.stream)) return out;
     flush_chain(ctx);
     kernels::gemm_tc(x, w, out, swiglu, ctx.tc_status, ctx.stream);

@@ -129,6 +129,13 @@ struct StepContext {
   // this pointer; the block then has nothing left to add.  Parts that ignore it lose nothing.
   float *residual_sink = nullptr;
   int64_t sink_rows = 0, sink_cols = 0;
+  // Set by a block that adds the results of several parts at once: 32-bit room for `parts_cap` results
+  // of [parts_rows, parts_cols] one behind the other.  A part whose last product hands back partial
+  // products (linear(..., parts_ok)) puts them here, from part `parts_used` on, so that what several parts
+  // leave is one run of parts that a single pass adds in order.
+  float *parts_pool = nullptr;
+  int parts_cap = 0, parts_used = 0;
+  int64_t parts_rows = 0, parts_cols = 0;
   // Set by the model for the last layer of a step that wants the logits of fewer rows than it has
   // tokens (a prompt whose last token alone is wanted): after that layer's mixer nothing but these
   // rows of the residual stream is read.  A block may then go on with those rows alone
