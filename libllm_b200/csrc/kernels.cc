@@ -373,8 +373,27 @@ int moe_tile_rows() {
   static auto f = resolve<int (*)()>("moe", "llm_moe_tile_rows");
   return f();
 }
-void moe_sort(const int *chosen, int n_rows, int n_experts, int *offsets, int *perm, int *tiles, cudaStream_t s) {
-  LLM_CALL("moe", llm_moe_sort, chosen, n_rows, n_experts, moe_tile_rows(), offsets, perm, tiles, s);
+void moe_sort(const int *chosen, int n_rows, int n_experts, int tile_rows, int *offsets, int *perm, int *tiles, cudaStream_t s) {
+  LLM_CALL("moe", llm_moe_sort, chosen, n_rows, n_experts, tile_rows, offsets, perm, tiles, s);
+}
+LLM_KERNEL("moe", llm_moe_gather, const void *, long long, const int *, int, int, int, void *, cudaStream_t)
+LLM_KERNEL("moe_tc", llm_moe_tc, const void *, const void *, const void *, const int *, const int *, const int *, const float *, int,
+           int, int, int, int, int, int, void *, float *, int *, cudaStream_t)
+bool moe_tc_supported(int width, int ff) {
+  static auto f = resolve<int (*)(int, int)>("moe_tc", "llm_moe_tc_supports");
+  return f(width, ff) != 0;
+}
+int moe_tc_tile_rows(int n_rows) {
+  static auto f = resolve<int (*)(int)>("moe_tc", "llm_moe_tc_tile_rows");
+  return f(n_rows);
+}
+void moe_tc(const Act &x, const void *up, const void *down, const int *offsets, const int *perm, const int *tiles,
+            const float *weight, int n_experts, int top, int width, int ff, int act, bool weight_on_output, void *xs, void *mid,
+            float *out, int *status, cudaStream_t s) {
+  const int n_rows = (int)x.rows * top;
+  LLM_CALL("moe", llm_moe_gather, x.data, (long long)x.ld, perm, n_rows, top, width, xs, s);
+  LLM_CALL("moe_tc", llm_moe_tc, xs, up, down, offsets, perm, tiles, weight, (int)x.rows, n_experts, top, width, ff, act,
+           weight_on_output ? 1 : 0, mid, out, status, s);
 }
 void moe_rows(const Act &x, const void *up, const void *down, const int *chosen, const float *weight, int top, int width, int ff,
               int act, bool weight_on_output, float *out, cudaStream_t s) {

@@ -117,7 +117,7 @@ void activation(const Act &in, const Act &out, int act, cudaStream_t s);
 // logits [T, E] 32-bit -> chosen [T * top], weight [T * top]; score 0 sigmoid, 1 softmax
 void moe_route(const Act &logits, int n_experts, int top, int score, bool renormalize, int *chosen, float *weight, cudaStream_t s);
 int moe_tile_rows();
-void moe_sort(const int *chosen, int n_rows, int n_experts, int *offsets, int *perm, int *tiles, cudaStream_t s);
+void moe_sort(const int *chosen, int n_rows, int n_experts, int tile_rows, int *offsets, int *perm, int *tiles, cudaStream_t s);
 // x [T, width]; up [E, ff, width], down [E, width, ff] in x's type; out [top, T, width] 32-bit
 void moe_rows(const Act &x, const void *up, const void *down, const int *chosen, const float *weight, int top, int width, int ff,
               int act, bool weight_on_output, float *out, cudaStream_t s);
@@ -125,6 +125,13 @@ bool moe_grouped_supported(int width, int ff);
 void moe_grouped(const Act &x, const void *up, const void *down, const int *offsets, const int *perm, const int *tiles,
                  const float *weight, int n_experts, int top, int width, int ff, int act, bool weight_on_output, void *mid,
                  float *out, cudaStream_t s);
+// The same on tcgen05 (csrc/moe_tc.cu): the table of tiles must have moe_tc_tile_rows(rows) rows to a tile;
+// xs [T * top, width] receives the tokens' rows in sorted order.
+bool moe_tc_supported(int width, int ff);
+int moe_tc_tile_rows(int n_rows);
+void moe_tc(const Act &x, const void *up, const void *down, const int *offsets, const int *perm, const int *tiles,
+            const float *weight, int n_experts, int top, int width, int ff, int act, bool weight_on_output, void *xs, void *mid,
+            float *out, int *status, cudaStream_t s);
 // ---- sampling
 void argmax(const float *logits, long long stride, int n_rows, int vocab, int *out, cudaStream_t s);
 void sample(const float *logits, long long stride, int n_rows, int vocab, float temperature, int top_k, float top_p,

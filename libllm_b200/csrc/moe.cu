@@ -370,3 +370,31 @@ LLM_EXPORT int llm_activation(int in_dtype, int dtype, const void *in, void *out
   LLM_CHECK_LAUNCH("activation");
   return LLM_OK;
 }
+
+// ---------------------------------------------------------------- the tokens' rows in sorted order
+// xs[place] = x[perm[place] / top], 16 bytes to a thread: the operand of the tensor-memory form of the first
+// product (csrc/moe_tc.cu), whose loads want the rows of a tile one behind the other.
+__global__ void moe_gather_kernel(const uint4 *__restrict__ x, long long ldx16, const int *__restrict__ perm, int top,
+                                  int width16, size_t total, uint4 *__restrict__ xs) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t place = idx / width16;
+    const int c = (int)(idx - place * width16);
+    xs[idx] = x[(size_t)(perm[place] / top) * ldx16 + c];
+  }
+}
+
+LLM_EXPORT int llm_moe_gather(const void *x, long long ldx, const int *perm, int n_rows, int top, int width, void *xs,
+                              cudaStream_t stream) {
+  if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && top > 0 && width % 8 == 0 && ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)xs % 16 == 0,
+              "moe_gather: rows of bfloat16 in multiples of 8, 16-byte aligned");
+  const size_t total = (size_t)n_rows * (width / 8);
+  size_t blocks = (total + 255) / 256;
+  if (blocks > (size_t)sm_count() * 32) blocks = (size_t)sm_count() * 32;
+  llm_launch_after(moe_gather_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const uint4 *)x, ldx / 8, perm, top, width / 8, total,
+             (uint4 *)xs);
+  LLM_CHECK_LAUNCH("moe_gather");
+  return LLM_OK;
+}

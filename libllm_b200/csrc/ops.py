@@ -253,7 +253,8 @@ def moe_route(logits: torch.Tensor, top: int, score: str = "sigmoid", renormaliz
 def moe_experts(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
                 act: str = "gelu", weight_on: str = "input", grouped: bool = False) -> torch.Tensor:
     """out [top, T, width] 32-bit: the chosen experts' down(act(up(x))), a row per choice.  up [E, ff, width],
-    down [E, width, ff].  ``grouped``: rows sorted by expert and multiplied on the tensor cores (bfloat16)."""
+    down [E, width, ff].  ``grouped``: rows sorted by expert and multiplied on the tensor cores (bfloat16), True with
+    mma.sync, "tc" with tcgen05."""
     _on_gpu(x, up, down, chosen, weight)
     T, width = x.shape
     E, ff = up.shape[0], up.shape[1]
@@ -268,16 +269,30 @@ def moe_experts(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, chosen: t
               ACTIVATIONS[act], 1 if weight_on == "output" else 0, _ptr(out), _stream())
         return out
     assert x.dtype == torch.bfloat16
-    lib = build.load("moe")
-    lib.llm_moe_tile_rows.restype = c_int
-    tile = lib.llm_moe_tile_rows()
     n_rows = T * top
+    if grouped == "tc":
+        lib = build.load("moe_tc")
+        lib.llm_moe_tc_tile_rows.restype, lib.llm_moe_tc_tile_rows.argtypes = c_int, [c_int]
+        tile = lib.llm_moe_tc_tile_rows(n_rows)
+    else:
+        lib = build.load("moe")
+        lib.llm_moe_tile_rows.restype = c_int
+        tile = lib.llm_moe_tile_rows()
     offsets = torch.empty(E + 1, dtype=torch.int32, device=x.device)
     perm = torch.empty(n_rows, dtype=torch.int32, device=x.device)
     tiles = torch.empty(1 + 2 * (min(E, n_rows) + n_rows // tile), dtype=torch.int32, device=x.device)
     mid = torch.empty(n_rows, ff, dtype=torch.bfloat16, device=x.device)
     _call("moe", "llm_moe_sort", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
           _ptr(chosen), n_rows, E, tile, _ptr(offsets), _ptr(perm), _ptr(tiles), _stream())
+    if grouped == "tc":
+        xs = torch.empty(n_rows, width, dtype=torch.bfloat16, device=x.device)
+        _call("moe", "llm_moe_gather", [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+              _ptr(x), x.stride(0), _ptr(perm), n_rows, top, width, _ptr(xs), _stream())
+        _call("moe_tc", "llm_moe_tc", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                       c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+              _ptr(xs), _ptr(up), _ptr(down), _ptr(offsets), _ptr(perm), _ptr(tiles), _ptr(weight), T, E, top, width, ff,
+              ACTIVATIONS[act], 1 if weight_on == "output" else 0, _ptr(mid), _ptr(out), _ptr(tc_status(x.device)), _stream())
+        return out
     _call("moe", "llm_moe_grouped", [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
           _ptr(x), x.stride(0), _ptr(up), _ptr(down), _ptr(offsets), _ptr(perm), _ptr(tiles), _ptr(weight), T, E, top, width,

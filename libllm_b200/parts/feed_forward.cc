@@ -121,6 +121,7 @@ class RoutedFeedForward : public FeedForward {
   std::vector<std::string> kernel_families() const override {
     std::vector<std::string> fams = product_families(env_.dtype);
     fams.push_back("moe");
+    if (env_.dtype == DType::BF16 && fast_switches().moe_tc && hidden_ % 8 == 0 && inter_ % 8 == 0) fams.push_back("moe_tc");
     if (shared_)
       for (auto &f : shared_->kernel_families()) fams.push_back(f);
     return fams;
@@ -143,14 +144,24 @@ class RoutedFeedForward : public FeedForward {
     float *weight = ctx.arena->alloc_n<float>((size_t)n_rows);
     kernels::moe_route(z, experts_, top_, score_, renormalize_, chosen, weight, ctx.stream);
     Act out = ctx.arena->act(DType::F32, T, hidden_, top_ + (s_own ? s.parts : 0));
-    if (x.dtype == DType::BF16 && kernels::moe_grouped_supported((int)hidden_, (int)inter_) && x.ld % 8 == 0 &&
-        (uintptr_t)x.data % 16 == 0) {
+    const bool aligned = x.dtype == DType::BF16 && x.ld % 8 == 0 && (uintptr_t)x.data % 16 == 0;
+    if (aligned && fast_switches().moe_tc && kernels::available("moe_tc") && kernels::moe_tc_supported((int)hidden_, (int)inter_)) {
+      const int tile = kernels::moe_tc_tile_rows(n_rows);
+      int *offsets = ctx.arena->alloc_n<int>((size_t)experts_ + 1);
+      int *perm = ctx.arena->alloc_n<int>((size_t)n_rows);
+      int *tiles = ctx.arena->alloc_n<int>(1 + 2 * ((size_t)std::min(experts_, n_rows) + (size_t)(n_rows / tile)));
+      void *xs = ctx.arena->alloc((size_t)n_rows * (size_t)hidden_ * 2);
+      void *mid = ctx.arena->alloc((size_t)n_rows * (size_t)inter_ * 2);
+      kernels::moe_sort(chosen, n_rows, experts_, tile, offsets, perm, tiles, ctx.stream);
+      kernels::moe_tc(x, w_up_.get(), w_down_.get(), offsets, perm, tiles, weight, experts_, top_, (int)hidden_, (int)inter_, act_,
+                      weight_on_output_, xs, mid, (float *)out.data, ctx.tc_status, ctx.stream);
+    } else if (aligned && kernels::moe_grouped_supported((int)hidden_, (int)inter_)) {
       const int tile = kernels::moe_tile_rows();
       int *offsets = ctx.arena->alloc_n<int>((size_t)experts_ + 1);
       int *perm = ctx.arena->alloc_n<int>((size_t)n_rows);
       int *tiles = ctx.arena->alloc_n<int>(1 + 2 * ((size_t)std::min(experts_, n_rows) + (size_t)(n_rows / tile)));
       void *mid = ctx.arena->alloc((size_t)n_rows * (size_t)inter_ * 2);
-      kernels::moe_sort(chosen, n_rows, experts_, offsets, perm, tiles, ctx.stream);
+      kernels::moe_sort(chosen, n_rows, experts_, tile, offsets, perm, tiles, ctx.stream);
       kernels::moe_grouped(x, w_up_.get(), w_down_.get(), offsets, perm, tiles, weight, experts_, top_, (int)hidden_, (int)inter_,
                            act_, weight_on_output_, mid, (float *)out.data, ctx.stream);
     } else {

@@ -30,6 +30,7 @@ const FastSwitches &fast_switches() {
     f.library_gemm = !off("LIBLLM_B200_NO_LIBRARY_GEMM");
     f.gemm_chain = off("LIBLLM_B200_GEMM_CHAIN");      // set: on (measured no faster than the launches it replaces)
     f.add_in_product = !off("LIBLLM_B200_NO_ADD_IN_PRODUCT");
+    f.moe_tc = !off("LIBLLM_B200_NO_MOE_TC");
     f.tc_tokens = num("LIBLLM_B200_TC_TOKENS", 256);
     f.fused_gate_up_tokens = num("LIBLLM_B200_FUSED_GATE_UP_TOKENS", 1024);
     f.gemv_tokens = num("LIBLLM_B200_GEMV_TOKENS", 0);

@@ -14,6 +14,7 @@ namespace llm {
 struct FastSwitches {
   bool gemm_tc = true, gemv = true, decode_attention = true, prefill_attention = true, prefill_attention_tc = true,
        decode_attention_tc = true, library_gemm = true;
+  bool moe_tc = true;                  // the experts' products on tcgen05 (csrc/moe_tc.cu) rather than mma.sync
   bool add_in_product = true;          // prompt steps: the library product adds its result to the residual stream itself
   bool gemm_chain = false;             // queue a decoding step's products and norms into single launches (parts/chain.h)
   int tc_tokens = 256;                 // steps of up to this many tokens take the tcgen05 product

@@ -195,8 +195,9 @@ def test_choice_of_experts(E, top, score, renorm):
         assert torch.equal(idx2, idx) and torch.equal(val2, val)
 
 
-@pytest.mark.parametrize("dtype,grouped", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
-@pytest.mark.parametrize("T,E,top,width,ff", [(1, 4, 2, 64, 32), (37, 5, 1, 72, 24), (300, 3, 2, 48, 40), (150, 16, 3, 128, 136)])
+@pytest.mark.parametrize("dtype,grouped", [("float32", False), ("bfloat16", False), ("bfloat16", True), ("bfloat16", "tc")])
+@pytest.mark.parametrize("T,E,top,width,ff", [(1, 4, 2, 64, 32), (37, 5, 1, 72, 24), (300, 3, 2, 48, 40), (150, 16, 3, 128, 136),
+                                              (700, 6, 2, 256, 200)])
 def test_experts_products(dtype, grouped, T, E, top, width, ff):
     """Rows by expert: more rows than a tile holds for one expert, experts that nobody chose, one row."""
     from libllm_b200.csrc import ops
