@@ -30,9 +30,10 @@ constexpr int MT_THREADS = 192;
 constexpr int MT_ROWS = 128;
 constexpr int MT_A_BYTES = MT_ROWS * TC_BK * 2;
 
-__device__ __forceinline__ float mt_activate(float z, int kind) {
-  if (kind == 0) return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
-  if (kind == 1) return 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+template <int KIND>
+__device__ __forceinline__ float mt_activate(float z) {
+  if (KIND == 0) return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
+  if (KIND == 1) return 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
   return z / (1.f + expf(-z));
 }
 
@@ -46,14 +47,18 @@ struct MtShape {
   static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + 256;
 };
 
-template <int TN>
+// ACT: the activation of the first product (csrc/moe.cu numbers them), or -1 for the second product.  The kind of
+// product and the activation are the compiler's to know: with them as arguments the epilogue's loop was
+// branches around every element, and the sixteen values of a load were worked through one after the other.
+template <int TN, int ACT>
 __global__ void __launch_bounds__(MT_THREADS, 1)
 moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, int N, int K,
               const int *__restrict__ offsets, const int *__restrict__ perm, const int *__restrict__ tiles,
-              const float *__restrict__ weight, int n_tokens, int top, int act, int weight_on, int second,
+              const float *__restrict__ weight, int n_tokens, int top, int weight_on,
               __nv_bfloat16 *__restrict__ mid, float *__restrict__ out, int *status) {
   using S = MtShape<TN>;
   constexpr int STAGES = S::STAGES;
+  constexpr bool SECOND = ACT < 0;
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   unsigned long long *bars = (unsigned long long *)(smem + (size_t)STAGES * S::STAGE_BYTES);
@@ -173,28 +178,46 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
       const int tt = tile / row_tiles, row_tile = tile - tt * row_tiles;
       const int expert = tiles[1 + 2 * tt], place0 = tiles[2 + 2 * tt];
       const int count = min(TN, offsets[expert + 1] - place0);
+      // The tile's rows: where each one's result goes and its weight, a row to a lane (asked for before the
+      // accumulator is waited for, handed round by shuffles in the loop: no load stands between two stores).
+      int my_row[TN / 32];
+      float my_w[TN / 32];
+#pragma unroll
+      for (int j = 0; j < TN / 32; ++j) {
+        const int tok = j * 32 + lane;
+        const int id = tok < count ? perm[place0 + tok] : 0;
+        my_w[j] = tok < count ? weight[id] : 0.f;
+        my_row[j] = SECOND ? (id % top) * n_tokens + id / top : place0 + tok;
+      }
       const int acc = iter & 1;
       const unsigned acc_phase = (iter >> 1) & 1;
       ok = __all_sync(0xffffffffu, mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, status, 44));
       if (!ok) break;
       tc_fence_after();
       const int f = row_tile * MT_ROWS + quarter * 32 + lane;       // the weight row = output feature
-#pragma unroll 1
-      for (int c0 = 0; c0 < count; c0 += 16) {
-        float v[16];
-        tc_ld16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * TN + c0), v);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int tok = c0 + i;
-          if (tok < count && f < N) {
-            const int place = place0 + tok;
-            const int id = perm[place];
-            if (!second) {
-              const float w = weight[id];
-              const float y = weight_on == 0 ? mt_activate(w * v[i], act) : w * mt_activate(v[i], act);
-              mid[(size_t)place * N + f] = __float2bfloat16_rn(y);
+      for (int c0 = 0; c0 < TN; c0 += 16) {
+        if (c0 < count) {                                            // the same in all lanes
+          float v[16];
+          tc_ld16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(acc * TN + c0), v);
+          // all sixteen values first, then their stores: the values do not wait for one another
+          float y[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if (SECOND) {
+              y[i] = v[i];
             } else {
-              out[((size_t)(id % top) * n_tokens + id / top) * N + f] = v[i];
+              const float w = __shfl_sync(0xffffffffu, my_w[c0 >> 5], (c0 & 31) + i);
+              const float a = mt_activate<SECOND ? 0 : ACT>(weight_on == 0 ? w * v[i] : v[i]);
+              y[i] = weight_on == 0 ? a : w * a;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int row = __shfl_sync(0xffffffffu, my_row[c0 >> 5], (c0 & 31) + i);
+            if (c0 + i < count && f < N) {
+              if (SECOND) out[(size_t)row * N + f] = y[i];
+              else mid[(size_t)row * N + f] = __float2bfloat16_rn(y[i]);
             }
           }
         }
@@ -216,22 +239,22 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
   }
 }
 
-template <int TN>
+template <int TN, int ACT>
 int launch_moe_tc(const void *a, long long n_rows, const void *w, int n_experts, int N, int K, const int *offsets,
-                  const int *perm, const int *tiles, const float *weight, int n_tokens, int top, int act, int weight_on,
-                  int second, void *mid, float *out, int *status, cudaStream_t stream) {
+                  const int *perm, const int *tiles, const float *weight, int n_tokens, int top, int weight_on, void *mid,
+                  float *out, int *status, cudaStream_t stream) {
   using S = MtShape<TN>;
   CUtensorMap map_w, map_x;
   int rc = get_map(w, (long long)n_experts * N, K, K, 64, &map_w);
   if (rc != LLM_OK) return rc;
   rc = get_map(a, n_rows, K, K, TN, &map_x);
   if (rc != LLM_OK) return rc;
-  auto kern = moe_tc_kernel<TN>;
+  auto kern = moe_tc_kernel<TN, ACT>;
   LLM_CHECK_CUDA(llm_allow_smem(kern, S::SMEM), "moe_tc attribute");
   const long long most = ((long long)(n_experts < n_rows ? n_experts : n_rows) + n_rows / TN) * ((N + MT_ROWS - 1) / MT_ROWS);
   const int grid = (int)(most < sm_count() ? most : sm_count());
   LLM_CHECK_CUDA(llm_launch_after(kern, dim3(grid), dim3(MT_THREADS), S::SMEM, stream, map_w, map_x, N, K, offsets, perm, tiles, weight,
-                            n_tokens, top, act, weight_on, second, (__nv_bfloat16 *)mid, out, status),
+                            n_tokens, top, weight_on, (__nv_bfloat16 *)mid, out, status),
                  "moe_tc launch");
   return LLM_OK;
 }
@@ -254,18 +277,20 @@ LLM_EXPORT int llm_moe_tc(const void *xs, const void *up, const void *down, cons
   LLM_REQUIRE((uintptr_t)xs % 16 == 0 && (uintptr_t)up % 16 == 0 && (uintptr_t)down % 16 == 0 && (uintptr_t)mid % 16 == 0,
               "moe_tc: operands must be 16-byte aligned");
   LLM_REQUIRE((long long)n_experts * (ff > width ? ff : width) < (1ll << 31), "moe_tc: the stacked weights have too many rows");
+  LLM_REQUIRE(act >= 0 && act <= 2, "moe_tc: unknown activation %d", act);
   const long long n_rows = (long long)n_tokens * top;
-  int rc;
-  if (llm_moe_tc_tile_rows((int)n_rows) == 32) {
-    rc = launch_moe_tc<32>(xs, n_rows, up, n_experts, ff, width, offsets, perm, tiles, weight, n_tokens, top, act, weight_on, 0, mid,
-                           nullptr, status, stream);
-    if (rc != LLM_OK) return rc;
-    return launch_moe_tc<32>(mid, n_rows, down, n_experts, width, ff, offsets, perm, tiles, weight, n_tokens, top, act, weight_on, 1,
-                             nullptr, out, status, stream);
-  }
-  rc = launch_moe_tc<128>(xs, n_rows, up, n_experts, ff, width, offsets, perm, tiles, weight, n_tokens, top, act, weight_on, 0, mid,
-                          nullptr, status, stream);
-  if (rc != LLM_OK) return rc;
-  return launch_moe_tc<128>(mid, n_rows, down, n_experts, width, ff, offsets, perm, tiles, weight, n_tokens, top, act, weight_on, 1,
-                            nullptr, out, status, stream);
+#define MT_FIRST(TN, ACT)                                                                                                    \
+  launch_moe_tc<TN, ACT>(xs, n_rows, up, n_experts, ff, width, offsets, perm, tiles, weight, n_tokens, top, weight_on, mid, nullptr, \
+                         status, stream)
+#define MT_BOTH(TN)                                                                                                          \
+  do {                                                                                                                       \
+    const int rc = act == 0 ? MT_FIRST(TN, 0) : act == 1 ? MT_FIRST(TN, 1) : MT_FIRST(TN, 2);                                \
+    if (rc != LLM_OK) return rc;                                                                                             \
+    return launch_moe_tc<TN, -1>(mid, n_rows, down, n_experts, width, ff, offsets, perm, tiles, weight, n_tokens, top, weight_on, \
+                                 nullptr, out, status, stream);                                                              \
+  } while (0)
+  if (llm_moe_tc_tile_rows((int)n_rows) == 32) MT_BOTH(32);
+  MT_BOTH(128);
+#undef MT_BOTH
+#undef MT_FIRST
 }
