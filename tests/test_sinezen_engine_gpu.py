@@ -203,3 +203,50 @@ def test_the_model_folder_route_and_the_command_line_description(tmp_path):
     with pytest.raises(WeightsError) as e:
         Engine.from_tensors(c, w, dtype="float32", max_tokens=256)
     assert e.value.missing == ["l1.mlp.e2.down"] and e.value.unexpected == ["l1.mlp.e7.up"]
+
+
+def sinezen_folder(tmp_path, name, seed):
+    import json
+    from helpers import write_safetensors
+    c = Z.CONFIGS[name]
+    w = Z.random_weights(c, seed)
+    (tmp_path / "config.json").write_text(json.dumps(c))
+    write_safetensors(str(tmp_path / "model.safetensors"), {k: v.to(torch.bfloat16) for k, v in w.items()})
+    return str(tmp_path), c, w
+
+
+def test_the_command_line_generates_from_a_sinezen_folder(tmp_path):
+    """``bin/llm generate`` picks the model by config.json's ``architecture`` and builds what it needs."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    folder, c, w = sinezen_folder(tmp_path, "Z4", 8)
+    prompt = Z.tokens(c, 7, 800)
+    out = subprocess.run([os.path.join(root, "bin", "llm"), "generate", "-m", folder, "--prompt-ids", ",".join(map(str, prompt)),
+                          "--max-new-tokens", "4", "--temperature", "0", "--dtype", "float32", "--no-stop"],
+                         capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr
+    got = [int(t) for t in out.stdout.strip().splitlines()[-1].split(",")]
+    seq = list(prompt)
+    for tok in got:
+        logits = P.forward(c, w, seq)[-1]
+        top2 = logits.topk(2)
+        assert tok == int(top2.indices[0]) or float(top2.values[0] - top2.values[1]) < 1e-3
+        seq.append(tok)
+    assert len(got) == 4
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_replay_of_a_sinezen_folder(dtype, tmp_path):
+    """``bin/trace_run`` on a folder: two unequal requests that start together and go on by single
+    tokens, then a third alone that uses their slots and pages again."""
+    from test_entry_points_gpu import collect, run_trace, trace_of
+    folder, c, w = sinezen_folder(tmp_path, "Z2", 9)
+    first = [("a", Z.tokens(c, 120, 1), 101), ("b", Z.tokens(c, 40, 2), 7)]
+    steps = trace_of(first)
+    steps += trace_of([("c", Z.tokens(c, 70, 3), 66)], first_step=len(steps))
+    out_dir = str(tmp_path / "out")
+    run_trace(folder, dtype, steps, out_dir, max_tokens=256)
+    got = collect(steps, out_dir, c["vocab"])
+    for rid, toks, _ in first + [("c", Z.tokens(c, 70, 3), 66)]:
+        Z.check_rows(got[rid], P.forward(c, w, toks), dtype, f"trace {rid}")
