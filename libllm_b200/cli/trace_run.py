@@ -28,15 +28,18 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder the logits files are written to")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64)")
+                    help="most tokens live requests hold at any time")
     ap.add_argument("--no-graphs", action="store_true", help="do not capture single-token steps as CUDA graphs")
     args = ap.parse_args(argv)
 
     from libllm_b200.engine import Engine, StepItem
 
     os.makedirs(args.out, exist_ok=True)
-    engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens, use_graphs=not args.no_graphs,
-                                max_seq_len=max(64, (args.max_tokens + 63) // 64 * 64))
+    # The cache hands out pages of 64 tokens, so every live request may hold up to 63 places it does not use:
+    # room for that is added for as many requests as a batch is likely to have.
+    longest = max(64, (args.max_tokens + 63) // 64 * 64)
+    engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=longest + 64 * 64, use_graphs=not args.no_graphs,
+                                max_seq_len=longest)
     slots = {}
     for line in sys.stdin:
         line = line.strip()

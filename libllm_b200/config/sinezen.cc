@@ -40,7 +40,7 @@ Json parse_mixer(const Json &layer, const std::string &where) {
   m.set("kv_heads", kv);
   m.set("dim", dim);
   m.set("vdim", r.integer_or("vdim", dim));
-  m.set("scale", r.number("scale"));
+  m.set("scale", r.number("scale", false));
   if (r.present("mask")) {
     ConfigReader mr(r.object("mask"), where + ": mixer.mask");
     Json mask = Json::object();

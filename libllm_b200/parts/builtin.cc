@@ -170,7 +170,7 @@ class Attention : public Mixer {
     d_ = (int)r.integer("head_dim");
     window_ = (int)r.integer_or("window", 0, 0);
     bias_ = r.boolean_or("bias", false);
-    scale_ = (float)r.number_or("scale", 1.0 / std::sqrt((double)d_));
+    scale_ = (float)r.number_or("scale", 1.0 / std::sqrt((double)d_), false);
     q_name_ = r.string("q");
     k_name_ = r.string("k");
     v_name_ = r.string("v");
@@ -197,7 +197,7 @@ class Attention : public Mixer {
     // rows of the stacked matrix: a multiple of 8, so that rows of the 32-bit product start on 32 bytes
     stacked_rows_ = (gate_offset_ + (gate_name_.empty() ? 0 : n_heads_) + 7) / 8 * 8;
     // the tiled attention kernels take heads whose values are as wide as their keys, in multiples of 16
-    plain_ = dv_ == d_ && d_ % 16 == 0 && d_ >= 16;
+    plain_ = dv_ == d_ && d_ % 16 == 0 && d_ >= 16 && scale_ > 0.f;
   }
 
   std::vector<TensorNeed> tensor_needs() const override {

@@ -40,6 +40,7 @@ def layer(mixer, mlp):
 # Z3: no loop at all, heads of 64 (the tensor-memory prompt kernel), a partial rotation, a mask longer
 #     than any test sequence in one layer and one of 96 in the other, three experts of eight.
 # Z4: one repetition of a loop (the input mix still applies), a rotation of all and of no channels.
+# Z5: widths that are multiples of 2 only (no 16-byte rows anywhere), a negative score scale.
 CONFIGS: Dict[str, dict] = {
     "Z1": dict(architecture="Sinezen", vocab=200, width=64, norm=dict(eps=1e-6),
                layers=[layer(attn(4, 2, 16, 16, 8, 8), dense(96)),
@@ -57,6 +58,10 @@ CONFIGS: Dict[str, dict] = {
                layers=[layer(attn(2, 1, 32, 32, 33, 32), dense(64)),
                        layer(attn(3, 3, 16, 24, None, None), moe(3, 3, 16, shared=16))],
                loop=dict(start=1, stop=2, times=1)),
+    "Z5": dict(architecture="Sinezen", vocab=77, width=50, norm=dict(eps=1e-5),
+               layers=[layer(attn(5, 5, 10, 6, 9, 6, scale=0.4), moe(3, 2, 22, shared=14)),
+                       layer(attn(3, 1, 18, 18, 20, 10, scale=-0.2), dense(34))],
+               loop=dict(start=0, stop=1, times=2)),
 }
 
 
