@@ -233,6 +233,22 @@ def qk_place(qkv: torch.Tensor, q_out: torch.Tensor, n_heads: int, n_kv: int, he
           1 if write_cache else 0, _stream())
 
 
+def concat_stream(resid: torch.Tensor, delta: Optional[torch.Tensor], other: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = [resid[t] + sum of delta's parts at t | other[t]]: 32-bit [T, H] inputs (delta [parts, T, H] or None),
+    out [T, 2H] float32 or bfloat16."""
+    _on_gpu(resid, delta, other, out)
+    T, H = resid.shape
+    assert resid.dtype == other.dtype == torch.float32 and resid.is_contiguous() and other.is_contiguous()
+    assert out.is_contiguous() and tuple(out.shape) == (T, 2 * H)
+    parts = 0
+    if delta is not None:
+        assert delta.dtype == torch.float32 and delta.is_contiguous() and tuple(delta.shape[-2:]) == (T, H)
+        parts = delta.shape[0] if delta.dim() == 3 else 1
+    _call("elementwise", "llm_concat_stream", [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+          _ptr(resid), _ptr(delta), parts, T * H, _ptr(other), _ptr(out), dtype_code(out.dtype), T, H, _stream())
+    return out
+
+
 # ------------------------------------------------------------------ routed feed-forward
 ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2}
 

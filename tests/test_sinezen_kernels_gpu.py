@@ -89,14 +89,16 @@ def test_projection_norm_rotation_and_append(dtype, H, G, d, dv, rot, extra):
 def planted_case(L, H, G, d, dv, block, seed=0):
     """Queries all near one direction u; the keys at every block's first position and at the
     position before it lie along u with a large length, so that each of them outweighs all others
-    together: a query sees its own block's first key and must not see the one before it."""
+    together: a query sees its own block's first key and must not see the one before it.  Without
+    a block it is the key at position 2 that stands out: every later query, hundreds of positions
+    on, still has to find it."""
     g = torch.Generator().manual_seed(seed)
     u = torch.randn(d, generator=g)
     u = u / u.norm()
     q = bf(u[None, None, :] * 4 + 0.3 * torch.randn(L, H, d, generator=g))
     k = 0.3 * torch.randn(L, G, d, generator=g)
     for p in range(L):
-        if block and (p % block == 0 or p % block == block - 1):
+        if (block and (p % block == 0 or p % block == block - 1)) or (not block and p == 2):
             k[p] = u * 6
     v = torch.randn(L, G, dv, generator=g)
     return q, bf(k), bf(v)
@@ -176,6 +178,29 @@ def test_tiled_prompt_and_decode_attention_under_a_block_mask(d, H, G, block):
                 ws_ml = torch.zeros(2 * H * n_splits * 2, device=DEV)
                 ops.attention_decode(qd, out, kc, vc, pos, table, H, G, d, PAGE, chunk, n_splits, None, 0.3, ws_o, ws_ml, block=block)
                 close(out.cpu().reshape(2, H, d), want, "bfloat16", f"single-token attention at {p0}, {p1}, {n_splits} splits")
+
+
+def test_a_far_key_outweighs_hundreds_of_near_ones():
+    """The planted case without a block: the result at position 229 is, to a few percent, the value at position 2."""
+    q, k, v = planted_case(230, 2, 1, 32, 32, None)
+    pos = torch.arange(230)
+    ref = P.attention_core(q, k, v, pos, pos, 0.4, None)
+    assert float((ref[229, 0] - v[2, 0].double()).abs().max()) < 0.1 * float(v[2, 0].abs().max())
+
+
+# ---------------------------------------------------------------- the stream beside the token rows
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("parts", [0, 1, 3])
+def test_stream_beside_the_token_rows(dtype, parts):
+    from libllm_b200.csrc import ops
+    T, H = 37, 52
+    g = torch.Generator().manual_seed(parts)
+    resid, other = torch.randn(T, H, generator=g), torch.randn(T, H, generator=g)
+    delta = torch.randn(parts, T, H, generator=g) if parts else None
+    out = torch.zeros(T, 2 * H, dtype=DT[dtype], device=DEV)
+    ops.concat_stream(resid.to(DEV), delta.to(DEV) if parts else None, other.to(DEV), out)
+    want = torch.cat([resid + (delta.sum(0) if parts else 0), other], 1)
+    close(out.cpu(), want.double(), dtype, "stream beside the token rows")
 
 
 # ---------------------------------------------------------------- routed feed-forward
