@@ -41,6 +41,8 @@ def layer(mixer, mlp):
 #     than any test sequence in one layer and one of 96 in the other, three experts of eight.
 # Z4: one repetition of a loop (the input mix still applies), a rotation of all and of no channels.
 # Z5: widths that are multiples of 2 only (no 16-byte rows anywhere), a negative score scale.
+# Z6: no routed layer, heads of 64 and of 32 with values as wide as keys (the tiled kernels in prompt and
+#     single-token steps): in bfloat16 every position has to lie inside the bound.
 CONFIGS: Dict[str, dict] = {
     "Z1": dict(architecture="Sinezen", vocab=200, width=64, norm=dict(eps=1e-6),
                layers=[layer(attn(4, 2, 16, 16, 8, 8), dense(96)),
@@ -62,7 +64,16 @@ CONFIGS: Dict[str, dict] = {
                layers=[layer(attn(5, 5, 10, 6, 9, 6, scale=0.4), moe(3, 2, 22, shared=14)),
                        layer(attn(3, 1, 18, 18, 20, 10, scale=-0.2), dense(34))],
                loop=dict(start=0, stop=1, times=2)),
+    "Z6": dict(architecture="Sinezen", vocab=180, width=96, norm=dict(eps=1e-5),
+               layers=[layer(attn(2, 1, 64, 64, 72, 32), dense(128)),
+                       layer(attn(4, 2, 32, 32, 40, 32, base=2e4, scale=0.15), None),
+                       layer(attn(3, 3, 48, 48, 500, 16), dense(72))],
+               loop=dict(start=1, stop=3, times=2)),
 }
+
+
+def is_routed(c: dict) -> bool:
+    return any(L["mlp"] and L["mlp"]["kind"] == "moe" for L in c["layers"])
 
 
 def tensor_shapes(c: dict) -> Dict[str, List[int]]:

@@ -42,7 +42,7 @@ def test_whole_prompts(name, dtype):
     for i, n in enumerate([1, 2, 3, 8, 9, 25, 34, 51, 64, 65, 101, 130, 203]):
         toks = Z.tokens(c, n, i)
         got = replay_batch(engine, [("r", toks, n)])["r"]
-        Z.check_rows(got, plain(name, c, w, toks), dtype, f"{name} whole {n}")
+        Z.check_rows(got, plain(name, c, w, toks), dtype, f"{name} whole {n}", routed=Z.is_routed(c))
     assert engine.pages_in_use() == [0] * len(engine.pages_in_use())
 
 
@@ -56,7 +56,7 @@ def test_prompt_then_single_tokens_agrees_with_the_whole_prompt(name, dtype):
         toks = Z.tokens(c, n, 20 + i)
         ref = plain(name, c, w, toks)
         got = replay_batch(engine, [("r", toks, n_prompt)])["r"]
-        Z.check_rows(got, ref, dtype, f"{name} {n_prompt} + {n - n_prompt} single tokens")
+        Z.check_rows(got, ref, dtype, f"{name} {n_prompt} + {n - n_prompt} single tokens", routed=Z.is_routed(c))
         if dtype == "float32":
             whole = replay_batch(engine, [("r", toks, n)])["r"]
             assert float(Z.row_errors(got, whole).max()) < Z.TOL[dtype], f"{name}: decoding differs from the whole prompt"
@@ -78,7 +78,7 @@ def test_portions_of_a_prompt(name, dtype):
             rows.append(torch.from_numpy(engine.step([StepItem(slot, toks[at:at + n], list(range(n)))])))
             at += n
         engine.close_sequence(slot)
-        Z.check_rows(torch.cat(rows), ref, dtype, f"{name} portions {sizes[:4]}...")
+        Z.check_rows(torch.cat(rows), ref, dtype, f"{name} portions {sizes[:4]}...", routed=Z.is_routed(c))
     engine.cache_check()
 
 
@@ -99,7 +99,7 @@ def test_unequal_batches_against_each_request_alone(name, dtype):
             reqs.append((f"b{b}r{j}", Z.tokens(c, total, 100 * b + j), p))
         got = replay_batch(engine, reqs)
         for rid, toks, p in reqs:
-            Z.check_rows(got[rid], plain(name, c, w, toks), dtype, f"{name} batch {b} {rid}")
+            Z.check_rows(got[rid], plain(name, c, w, toks), dtype, f"{name} batch {b} {rid}", routed=Z.is_routed(c))
             if dtype == "float32" and b == 0:
                 single = replay_batch(alone, [(rid, toks, p)])[rid]
                 assert float(Z.row_errors(got[rid], single).max()) < Z.TOL[dtype], f"{name} {rid}: the batch changes the result"
@@ -113,7 +113,7 @@ def test_long_decoding(name, dtype):
     engine, c, w = setup(name, dtype)
     toks = Z.tokens(c, 330, 77)
     got = replay_batch(engine, [("r", toks, 2)])["r"]
-    Z.check_rows(got, plain(name, c, w, toks), dtype, f"{name} long decoding")
+    Z.check_rows(got, plain(name, c, w, toks), dtype, f"{name} long decoding", routed=Z.is_routed(c))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -121,8 +121,8 @@ def test_first_tokens_beside_a_long_neighbour(dtype):
     engine, c, w = setup("Z1", dtype)
     short, long_ = Z.tokens(c, 3, 5), Z.tokens(c, 90, 6)
     both = replay_batch(engine, [("l", long_, 60), ("s", short, 1)])
-    Z.check_rows(both["s"], plain("Z1", c, w, short), dtype, "first tokens beside a long request")
-    Z.check_rows(both["l"], plain("Z1", c, w, long_), dtype, "long neighbour")
+    Z.check_rows(both["s"], plain("Z1", c, w, short), dtype, "first tokens beside a long request", routed=Z.is_routed(c))
+    Z.check_rows(both["l"], plain("Z1", c, w, long_), dtype, "long neighbour", routed=Z.is_routed(c))
 
 
 @pytest.mark.parametrize("name", NAMES)
@@ -147,7 +147,7 @@ def test_a_step_cut_into_launch_sequences(dtype):
     reqs = [("a", Z.tokens(c, 150, 1), 150), ("b", Z.tokens(c, 30, 2), 30)]
     got = replay_batch(engine, reqs)
     for rid, toks, _ in reqs:
-        Z.check_rows(got[rid], plain("Z2", c, w, toks), dtype, f"cut {rid}")
+        Z.check_rows(got[rid], plain("Z2", c, w, toks), dtype, f"cut {rid}", routed=Z.is_routed(c))
 
 
 @pytest.mark.parametrize("name", NAMES)
@@ -249,4 +249,4 @@ def test_trace_replay_of_a_sinezen_folder(dtype, tmp_path):
     run_trace(folder, dtype, steps, out_dir, max_tokens=256)
     got = collect(steps, out_dir, c["vocab"])
     for rid, toks, _ in first + [("c", Z.tokens(c, 70, 3), 66)]:
-        Z.check_rows(got[rid], P.forward(c, w, toks), dtype, f"trace {rid}")
+        Z.check_rows(got[rid], P.forward(c, w, toks), dtype, f"trace {rid}", routed=Z.is_routed(c))
