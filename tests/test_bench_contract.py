@@ -66,6 +66,9 @@ def test_the_benchmark_line_on_a_gpu():
     assert rec["config"]["layers"] == rec["config"]["layers_full"] == 16 and rec["config"]["global_batch"] == 8
     assert rec["gpu_launches"] >= 8 * 100
     assert abs(rec["value"] - 8 * 1000.0 / rec["ms_per_step"]) < 1.0
-    assert 0 < rec["e2e"]["value"] <= rec["value"] * 1.05 and rec["e2e"]["h2d_bytes_per_step"] > 0 and rec["e2e"]["d2h_bytes_per_step"] > 0
+    # the end-to-end rate cannot beat the device's own step; of eight timed steps one slow one moves the mean by
+    # several percent, so the bound is the median step's rate
+    device_rate = 8 * 1000.0 / min(rec["ms_per_step"], rec["ms_per_step_median"])
+    assert 0 < rec["e2e"]["value"] <= device_rate * 1.05 and rec["e2e"]["h2d_bytes_per_step"] > 0 and rec["e2e"]["d2h_bytes_per_step"] > 0
     assert 0.2 < rec["roofline"]["frac"] < 1.1 and 0.2 < rec["prefill"]["frac"] < 1.1 and rec["prefill"]["tokens"] == 2048
     assert 0.2 < rec["dominant_kernel"]["frac"] < 1.1
