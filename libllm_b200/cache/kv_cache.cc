@@ -136,7 +136,9 @@ void KVCache::commit(int slot, int new_len) {
     else continue;
     std::vector<int> drop;
     const int upto = std::min(first_needed / page_size_, (int)rec.pages[g].size());
-    for (int lp = 0; lp < upto; ++lp)
+    // pages that hold one of the first `sink` positions stay for as long as the sequence lives
+    const int kept = need.kind == "window" && need.sink > 0 ? (need.sink + page_size_ - 1) / page_size_ : 0;
+    for (int lp = kept; lp < upto; ++lp)
       if (rec.pages[g][(size_t)lp] >= 0) {
         drop.push_back(rec.pages[g][(size_t)lp]);
         rec.pages[g][(size_t)lp] = -1;
@@ -226,6 +228,7 @@ Json KVCache::info() const {
     g.set("v_dim", grp.need.v_dim);
     g.set("window", grp.need.window > 0 ? Json(grp.need.window) : Json());
     g.set("block", grp.need.block > 0 ? Json(grp.need.block) : Json());
+    g.set("sink", grp.need.sink > 0 ? Json(grp.need.sink) : Json());
     g.set("runs", Json::list(grp.runs));
     g.set("pages_in_use", grp.pool->in_use());
     g.set("pages_available", grp.pool->available());

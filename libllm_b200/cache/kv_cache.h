@@ -6,7 +6,8 @@
 // [runs, pages, kv_heads, page_size, k_dim] and V likewise with v_dim (no V when v_dim is 0).
 // A sequence holds, per group, a list mapping its logical pages (position / page_size) to pool
 // pages; a "window" group gives pages back as soon as every position in them has left the
-// window, a "block" group as soon as the sequence has grown past their block.  The reference keeps one growing tensor pair per layer for one rectangular batch
+// window (but for the pages of the first `sink` positions, which a window with kept first positions holds on to), a
+// "block" group as soon as the sequence has grown past their block.  The reference keeps one growing tensor pair per layer for one rectangular batch
 // (src/libllm/kv_cache.h:31-59, src/libllm/llama.cc:188-212).
 #pragma once
 #include <map>

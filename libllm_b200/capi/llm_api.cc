@@ -647,6 +647,7 @@ LLM_API int32_t llm_cachebook_init(llm_cachebook_t *c, llm_json_t *spec) {
         n.v_dim = (int)er.integer_or("v_dim", n.k_dim, 0);
         n.window = (int)er.integer_or("window", 0, 0);
         n.block = (int)er.integer_or("block", 0, 0);
+        n.sink = (int)er.integer_or("sink", 0, 0);
       }
       needs.push_back(n);
       has.push_back(e.is_object() ? 1 : 0);

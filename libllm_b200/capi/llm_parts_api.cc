@@ -42,6 +42,7 @@ class MapLoader : public Loader {
   MapLoader(const StateMap &s, DType engine) : Loader(engine), state_(s) {}
   void fetch_into(const TensorNeed &need, DType target, void *dst) const override { state_.fetch_into(need, target, dst); }
   bool has(const std::string &name) const override { return state_.has(name); }
+  std::vector<int64_t> shape_of(const std::string &name) const override { return state_.stored(name).shape; }
 
  private:
   const StateMap &state_;
@@ -138,12 +139,24 @@ LLM_API int32_t llm_part_describe(llm_part_t *p, llm_json_t *out) {
         cj.set("v_dim", c.v_dim);
         cj.set("window", c.window > 0 ? Json(c.window) : Json());
         cj.set("block", c.block > 0 ? Json(c.block) : Json());
+        cj.set("sink", c.sink > 0 ? Json(c.sink) : Json());
         j.set("cache", cj);
       } else {
         j.set("cache", Json());
       }
       Json st = Json::array();
       for (const auto &s : m->state_need()) {
+        Json o = Json::object();
+        o.set("name", s.name);
+        o.set("shape", Json::list(s.shape));
+        o.set("dtype", dtype_name(s.dtype));
+        st.push(o);
+      }
+      j.set("state", st);
+    }
+    if (Block *b = dynamic_cast<Block *>(h.part.get())) {
+      Json st = Json::array();
+      for (const auto &s : b->state_need()) {
         Json o = Json::object();
         o.set("name", s.name);
         o.set("shape", Json::list(s.shape));

@@ -187,6 +187,8 @@ void register_builtin_architectures() {
   register_architecture_unlocked(std::move(a));
   extern void register_sinezen_architecture();     // config/sinezen.cc
   register_sinezen_architecture();
+  extern void register_sesuzen_architecture();     // config/sesuzen.cc
+  register_sesuzen_architecture();
 }
 
 }  // namespace llm

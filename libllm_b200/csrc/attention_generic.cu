@@ -1,7 +1,8 @@
 // Causal grouped-query attention over the paged cache, any head size up to 256 (values may
 // have another width than keys), any number of heads and groups; optional sliding window,
 // optional block mask (a query sees only keys of its own block of `block` positions, blocks
-// counted from position 0), optional gate per (token, head) on the result (multiplied by
+// counted from position 0), optionally the first `sink` positions of the sequence kept visible
+// beyond the window (at their true positions), optional gate per (token, head) on the result (multiplied by
 // sigmoid(gate)); element type float or bfloat16, arithmetic in 32-bit.  One warp serves one (token, head): lanes take 32 keys at a time
 // for the scores, then 32 channels at a time for the weighted sum, with a running
 // maximum and sum (the online form of softmax, src/flint/cpu/softmax.cc:31-60).
@@ -65,7 +66,7 @@ attention_generic_kernel(const T *__restrict__ q, long long q_stride, T *__restr
                          const T *__restrict__ vcache, const int *__restrict__ tok_seq,
                          const int *__restrict__ tok_pos, const int *__restrict__ page_table,
                          int pt_stride, int n_tokens, int n_heads, int n_kv, int d, int dv, int page_size,
-                         int window, int block, float scale, const float *__restrict__ gate,
+                         int window, int block, int sink, float scale, const float *__restrict__ gate,
                          long long gate_stride, int vec) {
   __shared__ __align__(16) float q_s[WARPS][MAX_D];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -86,34 +87,39 @@ attention_generic_kernel(const T *__restrict__ q, long long q_stride, T *__restr
 #pragma unroll
   for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.f;
 
-  for (int kb = kstart; kb <= p; kb += 32) {
-    const int j = kb + lane;
-    const bool valid = j <= p;
-    float s = -INFINITY;
-    if (valid) {
-      const int page = pt[j / page_size];
-      const T *krow = kcache + (((size_t)page * n_kv + kvh) * page_size + (j % page_size)) * d;
-      s = dot_row(q_s[warp], krow, d, vec != 0) * scale;
-    }
-    const float m_new = fmaxf(m, warp_max(s));          // finite: lane 0 always holds a key
-    const float pj = valid ? expf(s - m_new) : 0.f;
-    const float alpha = expf(m - m_new);                // 0 on the first block (m = -inf)
-    l = l * alpha + warp_sum(pj);
-#pragma unroll
-    for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= alpha;
-    const int nvalid = min(32, p - kb + 1);
-    for (int jj = 0; jj < nvalid; ++jj) {
-      const float pv = __shfl_sync(0xffffffffu, pj, jj);
-      const int key = kb + jj;
-      const int page = pt[key / page_size];
-      const T *vrow = vcache + (((size_t)page * n_kv + kvh) * page_size + (key % page_size)) * dv;
-#pragma unroll
-      for (int i = 0; i < MAX_D / 32; ++i) {
-        const int c = lane + 32 * i;
-        if (c < dv) acc[i] = fmaf(pv, to_float(vrow[c]), acc[i]);
+  // two runs of keys: the kept first positions that lie before the window, then the window
+  const int sink_end = (window > 0 && block == 0) ? min(sink, kstart) : 0;
+  for (int run = sink_end > 0 ? 0 : 1; run < 2; ++run) {
+    const int k0 = run == 0 ? 0 : kstart, k1 = run == 0 ? sink_end : p + 1;
+    for (int kb = k0; kb < k1; kb += 32) {
+      const int j = kb + lane;
+      const bool valid = j < k1;
+      float s = -INFINITY;
+      if (valid) {
+        const int page = pt[j / page_size];
+        const T *krow = kcache + (((size_t)page * n_kv + kvh) * page_size + (j % page_size)) * d;
+        s = dot_row(q_s[warp], krow, d, vec != 0) * scale;
       }
+      const float m_new = fmaxf(m, warp_max(s));          // finite: lane 0 always holds a key
+      const float pj = valid ? expf(s - m_new) : 0.f;
+      const float alpha = expf(m - m_new);                // 0 on the first block (m = -inf)
+      l = l * alpha + warp_sum(pj);
+#pragma unroll
+      for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= alpha;
+      const int nvalid = min(32, k1 - kb);
+      for (int jj = 0; jj < nvalid; ++jj) {
+        const float pv = __shfl_sync(0xffffffffu, pj, jj);
+        const int key = kb + jj;
+        const int page = pt[key / page_size];
+        const T *vrow = vcache + (((size_t)page * n_kv + kvh) * page_size + (key % page_size)) * dv;
+#pragma unroll
+        for (int i = 0; i < MAX_D / 32; ++i) {
+          const int c = lane + 32 * i;
+          if (c < dv) acc[i] = fmaf(pv, to_float(vrow[c]), acc[i]);
+        }
+      }
+      m = m_new;
     }
-    m = m_new;
   }
   T *orow = out + (size_t)token * out_stride + (size_t)h * dv;
   float inv = 1.f / l;
@@ -129,12 +135,13 @@ LLM_EXPORT int llm_attention_generic(int dtype, const void *q, long long q_strid
                                      long long out_stride, const void *kcache, const void *vcache,
                                      const int *tok_seq, const int *tok_pos, const int *page_table,
                                      int pt_stride, int n_tokens, int n_heads, int n_kv, int d, int dv,
-                                     int page_size, int window, int block, float scale, const float *gate,
+                                     int page_size, int window, int block, int sink, float scale, const float *gate,
                                      long long gate_stride, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0, "attention: bad head counts %d/%d", n_heads, n_kv);
   LLM_REQUIRE(d > 0 && d <= MAX_D && dv > 0 && dv <= MAX_D, "attention: head sizes %d / %d are not supported (up to %d)", d, dv, MAX_D);
-  LLM_REQUIRE(window >= 0 && block >= 0, "attention: bad window or block");
+  LLM_REQUIRE(window >= 0 && block >= 0 && sink >= 0, "attention: bad window, block or number of kept first positions");
+  LLM_REQUIRE(sink == 0 || block == 0, "attention: kept first positions go with a window, not with a block mask");
   // 16-byte loads of key rows where rows start on such a boundary
   const int vec = (dtype == LLM_F32 ? d % 4 == 0 : d % 8 == 0) && (uintptr_t)kcache % 16 == 0;
   const long long warps = (long long)n_tokens * n_heads;
@@ -143,13 +150,13 @@ LLM_EXPORT int llm_attention_generic(int dtype, const void *q, long long q_strid
   if (dtype == LLM_F32) {
     attention_generic_kernel<float><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
         (const float *)q, q_stride, (float *)out, out_stride, (const float *)kcache, (const float *)vcache,
-        tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, n_kv, d, dv, page_size, window, block, scale,
+        tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, n_kv, d, dv, page_size, window, block, sink, scale,
         gate, gate_stride, vec);
   } else if (dtype == LLM_BF16) {
     attention_generic_kernel<__nv_bfloat16><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
         (const __nv_bfloat16 *)q, q_stride, (__nv_bfloat16 *)out, out_stride, (const __nv_bfloat16 *)kcache,
         (const __nv_bfloat16 *)vcache, tok_seq, tok_pos, page_table, pt_stride, n_tokens, n_heads, n_kv, d, dv,
-        page_size, window, block, scale, gate, gate_stride, vec);
+        page_size, window, block, sink, scale, gate, gate_stride, vec);
   } else {
     LLM_FAIL("attention: unknown dtype %d", dtype);
   }

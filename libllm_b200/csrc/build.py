@@ -48,6 +48,7 @@ FAMILIES: Dict[str, dict] = {
     "elementwise": dict(sources=["elementwise.cu"], headers=["common.cuh"]),
     "gemm_plain": dict(sources=["gemm_plain.cu"], headers=["common.cuh"]),
     "rope": dict(sources=["rope.cu"], headers=["common.cuh"]),
+    "recurrent": dict(sources=["recurrent.cu"], headers=["common.cuh"]),
     "attention_generic": dict(sources=["attention_generic.cu"], headers=["common.cuh"]),
     "sampling": dict(sources=["sampling.cu"], headers=["common.cuh"]),
     "moe": dict(sources=["moe.cu"], headers=["common.cuh", "mma_tiles.cuh"]),

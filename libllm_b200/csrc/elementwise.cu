@@ -14,7 +14,8 @@ LLM_DEFINE_LAST_ERROR(llm_elementwise_last_error)
 template <typename T>
 __global__ void embedding_kernel(const T *__restrict__ table, const int *__restrict__ tokens,
                                  const int *__restrict__ fed_tokens, const int *__restrict__ fed_rows,
-                                 float *__restrict__ out, int hidden, int vocab) {
+                                 float *__restrict__ out, int hidden, int vocab, const T *__restrict__ pos_table,
+                                 int pos_rows, const int *__restrict__ tok_pos) {
   grid_dependents_launch();
   grid_dependency_wait();
   const int t = blockIdx.x;
@@ -29,14 +30,24 @@ __global__ void embedding_kernel(const T *__restrict__ table, const int *__restr
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
   const T *row = table + (size_t)id * hidden;
   float *o = out + (size_t)t * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]);
+  if (pos_table == nullptr) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]);
+    return;
+  }
+  // a learned vector per position is added to the token's row (32-bit sum of the two stored values)
+  int p = tok_pos[t];
+  p = p < 0 ? 0 : (p >= pos_rows ? pos_rows - 1 : p);      // the host refuses sequences longer than the table
+  const T *prow = pos_table + (size_t)p * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]) + to_float(prow[i]);
 }
 
-LLM_EXPORT int llm_embedding(int dtype, const void *table, const int *tokens, const int *fed_tokens,
-                             const int *fed_rows, float *out, int n_tokens, int hidden, int vocab,
-                             cudaStream_t stream) {
+// pos_table [pos_rows, hidden] in the table's type with the tokens' positions tok_pos, or null: no position vectors.
+LLM_EXPORT int llm_embedding_pos(int dtype, const void *table, const int *tokens, const int *fed_tokens,
+                                 const int *fed_rows, float *out, int n_tokens, int hidden, int vocab,
+                                 const void *pos_table, int pos_rows, const int *tok_pos, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embedding: bad sizes");
+  LLM_REQUIRE(pos_table == nullptr || (pos_rows > 0 && tok_pos != nullptr), "embedding: position vectors come with the positions");
   LLM_REQUIRE((fed_tokens == nullptr) == (fed_rows == nullptr), "embedding: fed tokens come with their rows");
   int threads = hidden >= 1024 ? 256 : 128;
   // A step's first kernel after its descriptor has arrived, and launched so that it starts only
@@ -46,13 +57,21 @@ LLM_EXPORT int llm_embedding(int dtype, const void *table, const int *tokens, co
   // this one; with an overlapping launch here, a later kernel could in rare runs read the positions
   // of the step before last.)
   if (dtype == LLM_F32)
-    llm_launch_after(embedding_kernel<float>, n_tokens, threads, 0, stream, (const float *)table, tokens, fed_tokens, fed_rows, out, hidden, vocab);
+    llm_launch_after(embedding_kernel<float>, n_tokens, threads, 0, stream, (const float *)table, tokens, fed_tokens, fed_rows, out, hidden, vocab,
+                     (const float *)pos_table, pos_rows, tok_pos);
   else if (dtype == LLM_BF16)
-    llm_launch_after(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16 *)table, tokens, fed_tokens, fed_rows, out, hidden, vocab);
+    llm_launch_after(embedding_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16 *)table, tokens, fed_tokens, fed_rows, out, hidden, vocab,
+                     (const __nv_bfloat16 *)pos_table, pos_rows, tok_pos);
   else
     LLM_FAIL("embedding: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("embedding");
   return LLM_OK;
+}
+
+LLM_EXPORT int llm_embedding(int dtype, const void *table, const int *tokens, const int *fed_tokens,
+                             const int *fed_rows, float *out, int n_tokens, int hidden, int vocab,
+                             cudaStream_t stream) {
+  return llm_embedding_pos(dtype, table, tokens, fed_tokens, fed_rows, out, n_tokens, hidden, vocab, nullptr, 0, nullptr, stream);
 }
 
 // ---------------------------------------------------------------- small copies as kernels
@@ -262,6 +281,80 @@ LLM_EXPORT int llm_add_rmsnorm(float *resid, const void *delta, int delta_dtype,
   if (delta_dtype == LLM_BF16 && out_dtype == LLM_F32)
     return launch_add_rmsnorm<__nv_bfloat16, float>(resid, delta, n_parts, part_stride, weight, eps, out, rows, n_rows, hidden, stream);
   LLM_FAIL("add_rmsnorm: unknown dtypes %d, %d", delta_dtype, out_dtype);
+}
+
+// ---------------------------------------------------------------- add + layer norm
+// As add_rmsnorm, with the norm  out = (v - mean) / sqrt(var + eps) * w + b,  var the mean of the
+// squared deviations (two passes over the row, which is kept in shared memory; sums in 32-bit in
+// the block's fixed order).
+template <typename TD, typename TO, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+add_layernorm_kernel(float *__restrict__ resid, const TD *__restrict__ delta, int n_parts, size_t part_stride,
+                     const float *__restrict__ weight, const float *__restrict__ bias, float eps, TO *__restrict__ out,
+                     const int *__restrict__ rows, int hidden) {
+  extern __shared__ float row_buf[];   // hidden floats
+  __shared__ float scratch[THREADS / 32 + 1];
+  grid_dependents_launch();
+  grid_dependency_wait();
+  const int i = blockIdx.x;
+  const int r = rows ? rows[i] : i;
+  float *x = resid + (size_t)r * hidden;
+  float sum = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += THREADS) {
+    float v = x[c];
+    for (int p = 0; p < n_parts; ++p) v += to_float(delta[p * part_stride + (size_t)r * hidden + c]);
+    row_buf[c] = v;
+    if (!rows && n_parts > 0) x[c] = v;
+    sum += v;
+  }
+  if (!out) return;
+  const float mean = block_sum<THREADS>(sum, scratch) / (float)hidden;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += THREADS) {
+    const float dv = row_buf[c] - mean;
+    ss = fmaf(dv, dv, ss);
+  }
+  const float var = block_sum<THREADS>(ss, scratch) / (float)hidden;
+  const float inv = 1.f / sqrtf(var + eps);
+  TO *o = out + (size_t)i * hidden;
+  for (int c = threadIdx.x; c < hidden; c += THREADS)
+    o[c] = from_float<TO>((row_buf[c] - mean) * inv * weight[c] + (bias ? bias[c] : 0.f));
+}
+
+template <typename TD, typename TO>
+static int launch_add_layernorm(float *resid, const void *delta, int n_parts, size_t part_stride, const float *weight,
+                                const float *bias, float eps, void *out, const int *rows, int n_rows, int hidden,
+                                cudaStream_t stream) {
+  const size_t smem = (size_t)hidden * sizeof(float);
+  LLM_REQUIRE(smem <= 200 * 1024, "add_layernorm: a row of %d values does not fit shared memory", hidden);
+  if (hidden <= 1024) {
+    auto kern = add_layernorm_kernel<TD, TO, 128>;
+    llm_launch(kern, n_rows, 128, smem, stream, resid, (const TD *)delta, n_parts, part_stride, weight, bias, eps, (TO *)out, rows, hidden);
+  } else {
+    auto kern = add_layernorm_kernel<TD, TO, 512>;
+    if (smem > 48 * 1024) LLM_CHECK_CUDA(llm_allow_smem(kern, smem), "add_layernorm attribute");
+    llm_launch(kern, n_rows, 512, smem, stream, resid, (const TD *)delta, n_parts, part_stride, weight, bias, eps, (TO *)out, rows, hidden);
+  }
+  LLM_CHECK_LAUNCH("add_layernorm");
+  return LLM_OK;
+}
+
+LLM_EXPORT int llm_add_layernorm(float *resid, const void *delta, int delta_dtype, int n_parts, long long part_stride,
+                                 const float *weight, const float *bias, float eps, void *out, int out_dtype, const int *rows,
+                                 int n_rows, int hidden, cudaStream_t stream) {
+  if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && hidden > 0 && n_parts >= 0, "add_layernorm: bad sizes");
+  LLM_REQUIRE(out == nullptr || weight != nullptr, "add_layernorm: a norm needs its weight");
+  if (!delta) n_parts = 0;
+  if (delta_dtype == LLM_F32 && out_dtype == LLM_F32)
+    return launch_add_layernorm<float, float>(resid, delta, n_parts, part_stride, weight, bias, eps, out, rows, n_rows, hidden, stream);
+  if (delta_dtype == LLM_F32 && out_dtype == LLM_BF16)
+    return launch_add_layernorm<float, __nv_bfloat16>(resid, delta, n_parts, part_stride, weight, bias, eps, out, rows, n_rows, hidden, stream);
+  if (delta_dtype == LLM_BF16 && out_dtype == LLM_BF16)
+    return launch_add_layernorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, n_parts, part_stride, weight, bias, eps, out, rows, n_rows, hidden, stream);
+  if (delta_dtype == LLM_BF16 && out_dtype == LLM_F32)
+    return launch_add_layernorm<__nv_bfloat16, float>(resid, delta, n_parts, part_stride, weight, bias, eps, out, rows, n_rows, hidden, stream);
+  LLM_FAIL("add_layernorm: unknown dtypes %d, %d", delta_dtype, out_dtype);
 }
 
 // ---------------------------------------------------------------- rows of the stream picked out

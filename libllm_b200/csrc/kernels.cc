@@ -137,7 +137,10 @@ std::vector<std::string> loaded_libraries() {
 long long launches() { return g_launches.load(); }
 
 // ---------------------------------------------------------------- elementwise
-LLM_KERNEL("elementwise", llm_embedding, int, const void *, const int *, const int *, const int *, float *, int, int, int, cudaStream_t)
+LLM_KERNEL("elementwise", llm_embedding_pos, int, const void *, const int *, const int *, const int *, float *, int, int, int,
+           const void *, int, const int *, cudaStream_t)
+LLM_KERNEL("elementwise", llm_add_layernorm, float *, const void *, int, int, long long, const float *, const float *, float, void *,
+           int, const int *, int, int, cudaStream_t)
 LLM_KERNEL("elementwise", llm_copy_words, const int *, int *, int, cudaStream_t)
 LLM_KERNEL("elementwise", llm_gather_words, const int *, int, const int *, int, int *, cudaStream_t)
 LLM_KERNEL("elementwise", llm_add_rmsnorm, float *, const void *, int, int, long long, const float *, float, void *, int,
@@ -149,8 +152,16 @@ LLM_KERNEL("elementwise", llm_logit_transform, float *, long long, float, float,
 LLM_KERNEL("elementwise", llm_random_fill, void *, int, long long, unsigned long long, int, float, float, cudaStream_t)
 
 void embedding(DType dt, const void *table, const int *tokens, const int *fed_tokens, const int *fed_rows, float *out,
-               int n, int hidden, int vocab, cudaStream_t s) {
-  LLM_CALL("elementwise", llm_embedding, code(dt), table, tokens, fed_rows ? fed_tokens : nullptr, fed_rows, out, n, hidden, vocab, s);
+               int n, int hidden, int vocab, cudaStream_t s, const void *pos_table, int pos_rows, const int *tok_pos) {
+  LLM_CALL("elementwise", llm_embedding_pos, code(dt), table, tokens, fed_rows ? fed_tokens : nullptr, fed_rows, out, n, hidden, vocab,
+           pos_table, pos_rows, tok_pos, s);
+}
+void add_layernorm(float *resid, const Act *delta, const float *weight, const float *bias, float eps, void *out, DType out_dtype,
+                   const int *rows, int n_rows, int hidden, cudaStream_t s) {
+  const bool has = delta && delta->data;
+  LLM_CALL("elementwise", llm_add_layernorm, resid, has ? delta->data : nullptr, has ? code(delta->dtype) : 0,
+           has ? delta->parts : 0, has ? (long long)delta->part_stride : 0, weight, bias, eps, out, code(out_dtype), rows, n_rows,
+           hidden, s);
 }
 void copy_words(const int *src, int *dst, int n, cudaStream_t s) { LLM_CALL("elementwise", llm_copy_words, src, dst, n, s); }
 void gather_words(const int *src1, int n1, const int *src2, int n2, int *dst, cudaStream_t s) {
@@ -274,9 +285,19 @@ void qk_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, in
            pt_stride, kcache, vcache, page_size, write_cache ? 1 : 0, s);
 }
 
+LLM_KERNEL("rope", llm_kv_place, int, int, const void *, long long, void *, long long, int, int, int, int, int, const float *, float,
+           const int *, const int *, const int *, int, void *, void *, int, int, cudaStream_t)
+void kv_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, int dv, const float *bias, float v_eps,
+              const int *tok_seq, const int *tok_pos, const int *page_table, int pt_stride, void *kcache, void *vcache,
+              int page_size, bool write_cache, cudaStream_t s) {
+  LLM_CALL("rope", llm_kv_place, code(qkv.dtype), code(q_out.dtype), qkv.data, (long long)qkv.ld, q_out.data, (long long)q_out.ld,
+           (int)qkv.rows, n_heads, n_kv, d, dv, bias, v_eps, tok_seq, tok_pos, page_table, pt_stride, kcache, vcache, page_size,
+           write_cache ? 1 : 0, s);
+}
+
 // ---------------------------------------------------------------- attention
 LLM_KERNEL("attention_generic", llm_attention_generic, int, const void *, long long, void *, long long, const void *, const void *,
-           const int *, const int *, const int *, int, int, int, int, int, int, int, int, int, float, const float *, long long,
+           const int *, const int *, const int *, int, int, int, int, int, int, int, int, int, int, float, const float *, long long,
            cudaStream_t)
 LLM_KERNEL("attention_decode", llm_attention_decode_gated, const void *, long long, void *, long long, const void *, const void *,
            const int *, const int *, int, int, int, int, int, int, int, int, int, int, float, float *, float *, const float *,
@@ -296,9 +317,9 @@ LLM_KERNEL("attention_prefill_tc", llm_attention_prefill_tc, const void *, long 
 
 void attention_generic(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_seq, const int *tok_pos,
                        const int *page_table, int pt_stride, int n_heads, int n_kv, int d, int dv, int page_size, int window,
-                       int block, float scale, const float *gate, long long gate_stride, cudaStream_t s) {
+                       int block, float scale, const float *gate, long long gate_stride, cudaStream_t s, int sink) {
   LLM_CALL("attention_generic", llm_attention_generic, code(q.dtype), q.data, (long long)q.ld, out.data, (long long)out.ld, kc, vc,
-           tok_seq, tok_pos, page_table, pt_stride, (int)q.rows, n_heads, n_kv, d, dv, page_size, window, block, scale, gate,
+           tok_seq, tok_pos, page_table, pt_stride, (int)q.rows, n_heads, n_kv, d, dv, page_size, window, block, sink, scale, gate,
            gate_stride, s);
 }
 bool attention_decode_supported(int d, int group) {
@@ -358,9 +379,9 @@ LLM_KERNEL("moe", llm_activation, int, int, const void *, void *, long long, int
 LLM_KERNEL("moe", llm_moe_route, const float *, long long, int, int, int, int, int, int *, float *, cudaStream_t)
 LLM_KERNEL("moe", llm_moe_sort, const int *, int, int, int, int *, int *, int *, cudaStream_t)
 LLM_KERNEL("moe", llm_moe_rows, int, const void *, long long, const void *, const void *, const int *, const float *, int, int, int,
-           int, int, int, float *, cudaStream_t)
+           int, int, int, int, float *, cudaStream_t)
 LLM_KERNEL("moe", llm_moe_grouped, const void *, long long, const void *, const void *, const int *, const int *, const int *,
-           const float *, int, int, int, int, int, int, int, void *, float *, cudaStream_t)
+           const float *, int, int, int, int, int, int, int, int, void *, float *, cudaStream_t)
 void activation(const Act &in, const Act &out, int act, cudaStream_t s) {
   if (in.ld != in.cols || out.ld != out.cols) LLM_THROW(InvalidArg, "activation: rows must be dense");
   LLM_CALL("moe", llm_activation, code(in.dtype), code(out.dtype), in.data, out.data, (long long)(in.rows * in.cols), act, s);
@@ -378,7 +399,7 @@ void moe_sort(const int *chosen, int n_rows, int n_experts, int tile_rows, int *
 }
 LLM_KERNEL("moe", llm_moe_gather, const void *, long long, const int *, int, int, int, void *, cudaStream_t)
 LLM_KERNEL("moe_tc", llm_moe_tc, const void *, const void *, const void *, const int *, const int *, const int *, const float *, int,
-           int, int, int, int, int, int, void *, float *, int *, cudaStream_t)
+           int, int, int, int, int, int, int, void *, float *, int *, cudaStream_t)
 bool moe_tc_supported(int width, int ff) {
   static auto f = resolve<int (*)(int, int)>("moe_tc", "llm_moe_tc_supports");
   return f(width, ff) != 0;
@@ -389,16 +410,16 @@ int moe_tc_tile_rows(int n_rows) {
 }
 void moe_tc(const Act &x, const void *up, const void *down, const int *offsets, const int *perm, const int *tiles,
             const float *weight, int n_experts, int top, int width, int ff, int act, bool weight_on_output, void *xs, void *mid,
-            float *out, int *status, cudaStream_t s) {
+            float *out, int *status, cudaStream_t s, bool gated) {
   const int n_rows = (int)x.rows * top;
   LLM_CALL("moe", llm_moe_gather, x.data, (long long)x.ld, perm, n_rows, top, width, xs, s);
   LLM_CALL("moe_tc", llm_moe_tc, xs, up, down, offsets, perm, tiles, weight, (int)x.rows, n_experts, top, width, ff, act,
-           weight_on_output ? 1 : 0, mid, out, status, s);
+           weight_on_output ? 1 : 0, gated ? 1 : 0, mid, out, status, s);
 }
 void moe_rows(const Act &x, const void *up, const void *down, const int *chosen, const float *weight, int top, int width, int ff,
-              int act, bool weight_on_output, float *out, cudaStream_t s) {
+              int act, bool weight_on_output, float *out, cudaStream_t s, bool gated) {
   LLM_CALL("moe", llm_moe_rows, code(x.dtype), x.data, (long long)x.ld, up, down, chosen, weight, (int)x.rows, top, width, ff, act,
-           weight_on_output ? 1 : 0, out, s);
+           weight_on_output ? 1 : 0, gated ? 1 : 0, out, s);
 }
 bool moe_grouped_supported(int width, int ff) {
   static auto f = resolve<int (*)(int, int)>("moe", "llm_moe_grouped_supports");
@@ -406,9 +427,38 @@ bool moe_grouped_supported(int width, int ff) {
 }
 void moe_grouped(const Act &x, const void *up, const void *down, const int *offsets, const int *perm, const int *tiles,
                  const float *weight, int n_experts, int top, int width, int ff, int act, bool weight_on_output, void *mid,
-                 float *out, cudaStream_t s) {
+                 float *out, cudaStream_t s, bool gated) {
   LLM_CALL("moe", llm_moe_grouped, x.data, (long long)x.ld, up, down, offsets, perm, tiles, weight, (int)x.rows, n_experts, top,
-           width, ff, act, weight_on_output ? 1 : 0, mid, out, s);
+           width, ff, act, weight_on_output ? 1 : 0, gated ? 1 : 0, mid, out, s);
+}
+
+// ---------------------------------------------------------------- state carried from token to token
+LLM_KERNEL("recurrent", llm_causal_conv, int, const void *, long long, void *, long long, const float *, void *, const int *,
+           const int *, const int *, const int *, const int *, int, int, int, int, int, cudaStream_t)
+LLM_KERNEL("recurrent", llm_delta_rule, const float *, long long, int, int, int, int, int, int, const float *, const float *,
+           const float *, float, float, float *, float *, float *, long long, const int *, const int *, int, int, int, int, cudaStream_t)
+LLM_KERNEL("recurrent", llm_head_norm_gate, const float *, long long, const float *, const float *, long long, float, int, int, int,
+           void *, int, long long, cudaStream_t)
+void causal_conv(const Act &h, const Act &out, const float *weight, void *state, const int *tok_seq, const int *tok_pos,
+                 const int *seq_start, const int *seq_past, const int *seq_slot, int n_seqs, int taps, bool single_tokens,
+                 cudaStream_t s) {
+  if (h.dtype != out.dtype) LLM_THROW(InvalidArg, "causal_conv: input and output have one type");
+  LLM_CALL("recurrent", llm_causal_conv, code(h.dtype), h.data, (long long)h.ld, out.data, (long long)out.ld, weight, state, tok_seq,
+           tok_pos, seq_start, seq_past, seq_slot, (int)h.rows, n_seqs, (int)h.cols, taps, single_tokens ? 1 : 0, s);
+}
+void delta_rule(const Act &proj, int off_r, int off_k, int off_v, int off_a, int off_x1, int rank, const float *w2, const float *w0,
+                const float *a_bias, float decay_scale, float key_eps, float *prep, float *state, const Act &out,
+                const int *seq_start, const int *seq_slot, int n_seqs, int n_heads, int d, cudaStream_t s) {
+  if (proj.dtype != DType::F32 || out.dtype != DType::F32) LLM_THROW(InvalidArg, "delta_rule: projections and results are 32-bit");
+  LLM_CALL("recurrent", llm_delta_rule, (const float *)proj.data, (long long)proj.ld, off_r, off_k, off_v, off_a, off_x1, rank, w2, w0,
+           a_bias, decay_scale, key_eps, prep, state, (float *)out.data, (long long)out.ld, seq_start, seq_slot, (int)proj.rows,
+           n_seqs, n_heads, d, s);
+}
+void head_norm_gate(const Act &x, const float *weight, const float *gate, long long gate_stride, float eps, int n_heads, int dv,
+                    const Act &out, cudaStream_t s) {
+  if (x.dtype != DType::F32) LLM_THROW(InvalidArg, "head_norm_gate: the heads' results are 32-bit");
+  LLM_CALL("recurrent", llm_head_norm_gate, (const float *)x.data, (long long)x.ld, weight, gate, gate_stride, eps, (int)x.rows,
+           n_heads, dv, out.data, code(out.dtype), (long long)out.ld, s);
 }
 
 // ---------------------------------------------------------------- sampling

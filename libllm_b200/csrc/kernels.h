@@ -26,11 +26,15 @@ std::vector<std::string> loaded_libraries();
 
 // ---- elementwise
 void embedding(DType table_dtype, const void *table, const int *tokens, const int *fed_tokens, const int *fed_rows,
-               float *out, int n_tokens, int hidden, int vocab, cudaStream_t s);
+               float *out, int n_tokens, int hidden, int vocab, cudaStream_t s, const void *pos_table = nullptr, int pos_rows = 0,
+               const int *tok_pos = nullptr);   // pos_table [pos_rows, hidden] in the table's type: a learned vector per position, added
 void copy_words(const int *src, int *dst, int n, cudaStream_t s);
 void gather_words(const int *src1, int n1, const int *src2, int n2, int *dst, cudaStream_t s);
 void add_rmsnorm(float *resid, const Act *delta, const float *weight, float eps, void *out, DType out_dtype,
                  const int *rows, int n_rows, int hidden, cudaStream_t s);
+// The same pass with a layer norm: (v - mean) / sqrt(var + eps) * weight + bias (bias may be null).
+void add_layernorm(float *resid, const Act *delta, const float *weight, const float *bias, float eps, void *out, DType out_dtype,
+                   const int *rows, int n_rows, int hidden, cudaStream_t s);
 // out[i] = resid[rows[i]] + delta's parts at that row (32-bit)
 void gather_rows_add(const float *resid, const Act *delta, const int *rows, int n_rows, float *out, int hidden, cudaStream_t s);
 void swiglu(const Act &gu, void *out, DType out_dtype, cudaStream_t s);
@@ -83,13 +87,18 @@ void rope_cache_write(const Act &qkv, const Act &q_out, int n_heads, int n_kv, i
 void qk_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, int dv, const float *q_norm, const float *k_norm,
               float eps, const float *table, int table_rows, int rot_dim, const int *tok_seq, const int *tok_pos,
               const int *page_table, int pt_stride, void *kcache, void *vcache, int page_size, bool write_cache, cudaStream_t s);
+// Rows [q | k | v | ...] without a rotation: adds `bias` (one 32-bit value per stacked row; null: none), divides each
+// value head by its root mean square when v_eps >= 0, writes q and appends k, v to the cache.
+void kv_place(const Act &qkv, const Act &q_out, int n_heads, int n_kv, int d, int dv, const float *bias, float v_eps,
+              const int *tok_seq, const int *tok_pos, const int *page_table, int pt_stride, void *kcache, void *vcache,
+              int page_size, bool write_cache, cudaStream_t s);
 // ---- attention
 // Masks: `window` > 0, a query sees the last `window` keys; `block` > 0, only keys of its own block
-// of `block` positions counted from 0.  `gate` (32-bit, one value per token and head, row stride
+// of `block` positions counted from 0; `sink` > 0 (with a window): the first `sink` positions stay visible.  `gate` (32-bit, one value per token and head, row stride
 // gate_stride; null: none): the head's result is multiplied by sigmoid(gate).
 void attention_generic(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_seq, const int *tok_pos,
                        const int *page_table, int pt_stride, int n_heads, int n_kv, int d, int dv, int page_size, int window,
-                       int block, float scale, const float *gate, long long gate_stride, cudaStream_t s);
+                       int block, float scale, const float *gate, long long gate_stride, cudaStream_t s, int sink = 0);
 bool attention_decode_supported(int d, int group);
 void attention_decode(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                       int pt_stride, int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window,
@@ -112,26 +121,40 @@ void attention_prefill_tc(const Act &q, const Act &out, const void *kc, const vo
 // out[t, h, :] *= sigmoid(gate[t * gate_stride + h]) for heads of width dv
 void head_gate(const Act &out, const float *gate, long long gate_stride, int n_heads, int dv, cudaStream_t s);
 // ---- routed feed-forward (csrc/moe.cu)
-enum Activation { GeluErf = 0, GeluTanh = 1, Silu = 2 };
+enum Activation { GeluErf = 0, GeluTanh = 1, Silu = 2, Relu2 = 3 };
 void activation(const Act &in, const Act &out, int act, cudaStream_t s);
 // logits [T, E] 32-bit -> chosen [T * top], weight [T * top]; score 0 sigmoid, 1 softmax
 void moe_route(const Act &logits, int n_experts, int top, int score, bool renormalize, int *chosen, float *weight, cudaStream_t s);
 int moe_tile_rows();
 void moe_sort(const int *chosen, int n_rows, int n_experts, int tile_rows, int *offsets, int *perm, int *tiles, cudaStream_t s);
-// x [T, width]; up [E, ff, width], down [E, width, ff] in x's type; out [top, T, width] 32-bit
+// x [T, width]; up [E, ff, width], down [E, width, ff] in x's type; out [top, T, width] 32-bit.  `gated`: up is
+// [E, 2 ff, width], an expert's gate and up rows interleaved, and the expert is down(act(gate x) * up x).
 void moe_rows(const Act &x, const void *up, const void *down, const int *chosen, const float *weight, int top, int width, int ff,
-              int act, bool weight_on_output, float *out, cudaStream_t s);
+              int act, bool weight_on_output, float *out, cudaStream_t s, bool gated = false);
 bool moe_grouped_supported(int width, int ff);
 void moe_grouped(const Act &x, const void *up, const void *down, const int *offsets, const int *perm, const int *tiles,
                  const float *weight, int n_experts, int top, int width, int ff, int act, bool weight_on_output, void *mid,
-                 float *out, cudaStream_t s);
+                 float *out, cudaStream_t s, bool gated = false);
 // The same on tcgen05 (csrc/moe_tc.cu): the table of tiles must have moe_tc_tile_rows(rows) rows to a tile;
 // xs [T * top, width] receives the tokens' rows in sorted order.
 bool moe_tc_supported(int width, int ff);
 int moe_tc_tile_rows(int n_rows);
 void moe_tc(const Act &x, const void *up, const void *down, const int *offsets, const int *perm, const int *tiles,
             const float *weight, int n_experts, int top, int width, int ff, int act, bool weight_on_output, void *xs, void *mid,
-            float *out, int *status, cudaStream_t s);
+            float *out, int *status, cudaStream_t s, bool gated = false);
+// ---- state carried from token to token (csrc/recurrent.cu)
+// out = h + conv(h) over time per channel, weight [width, taps] 32-bit; state [slots, taps - 1, width] in h's type
+void causal_conv(const Act &h, const Act &out, const float *weight, void *state, const int *tok_seq, const int *tok_pos,
+                 const int *seq_start, const int *seq_past, const int *seq_slot, int n_seqs, int taps, bool single_tokens,
+                 cudaStream_t s);
+// The generalized delta rule over the 32-bit rows `proj` (offsets of r, k, v, the removal logits and the low-rank decay
+// input within a row); prep: scratch [tokens, heads, 3, d] floats; state [slots, heads, d, d] floats; out [tokens, heads * d].
+void delta_rule(const Act &proj, int off_r, int off_k, int off_v, int off_a, int off_x1, int rank, const float *w2, const float *w0,
+                const float *a_bias, float decay_scale, float key_eps, float *prep, float *state, const Act &out,
+                const int *seq_start, const int *seq_slot, int n_seqs, int n_heads, int d, cudaStream_t s);
+// out[t, h, :] = x / rms(x over the head; eps < 0: no norm) * weight (null: none) * sigmoid(gate) (null: none)
+void head_norm_gate(const Act &x, const float *weight, const float *gate, long long gate_stride, float eps, int n_heads, int dv,
+                    const Act &out, cudaStream_t s);
 // ---- sampling
 void argmax(const float *logits, long long stride, int n_rows, int vocab, int *out, cudaStream_t s);
 void sample(const float *logits, long long stride, int n_rows, int vocab, float temperature, int top_k, float top_p,

@@ -9,6 +9,9 @@
 // row multiplies either the expert's input or its output.  Since up has no bias, up(w x) = w up(x),
 // so "input" is applied to the 32-bit result of the first product, before the activation, and
 // "output" after it (down is linear too); neither rounds a scaled input to 16 bits.
+// Gated experts, down(act(gate(x)) * up(x)): `up` then holds both matrices of an expert, rows
+// interleaved ([experts, 2 ff, width]: row 2n of gate, row 2n + 1 of up), so that a tile of the first
+// product holds a feature's two halves side by side; the weight goes on the output.
 //
 // Two forms of the products:
 //  * moe_rows_kernel: one CTA per row, both products on the CUDA cores in 32-bit arithmetic
@@ -27,11 +30,12 @@
 
 LLM_DEFINE_LAST_ERROR(llm_moe_last_error)
 
-enum { ACT_GELU_ERF = 0, ACT_GELU_TANH = 1, ACT_SILU = 2 };
+enum { ACT_GELU_ERF = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_RELU2 = 3 };
 
 __device__ __forceinline__ float activate(float z, int kind) {
   if (kind == ACT_GELU_ERF) return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
   if (kind == ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+  if (kind == ACT_RELU2) return z > 0.f ? z * z : 0.f;     // the square of max(z, 0)
   return z / (1.f + expf(-z));
 }
 
@@ -162,7 +166,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_rows_kernel(const T *__restrict__ x, long long ldx, const T *__restrict__ up, const T *__restrict__ down,
                 const int *__restrict__ chosen, const float *__restrict__ weight, int n_tokens, int top, int width, int ff,
-                int act, int weight_on, float *__restrict__ out) {
+                int act, int weight_on, int gated, float *__restrict__ out) {
   extern __shared__ float shf[];               // x row [width], hidden [ff]
   float *xs = shf, *hs = shf + width;
   grid_dependents_launch();
@@ -173,8 +177,14 @@ moe_rows_kernel(const T *__restrict__ x, long long ldx, const T *__restrict__ up
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int c = threadIdx.x; c < width; c += 256) xs[c] = to_float(x[(size_t)t * ldx + c]);
   __syncthreads();
-  const T *wu = up + (size_t)e * ff * width;
+  const T *wu = up + (size_t)e * ff * width * (gated ? 2 : 1);
   for (int n = warp; n < ff; n += 8) {
+    if (gated) {
+      const float g = dot_cols(wu + (size_t)(2 * n) * width, xs, width, lane);
+      const float u = dot_cols(wu + (size_t)(2 * n + 1) * width, xs, width, lane);
+      if (lane == 0) hs[n] = w * (activate(g, act) * u);
+      continue;
+    }
     const float v = dot_cols(wu + (size_t)n * width, xs, width, lane);
     if (lane == 0) hs[n] = weight_on == 0 ? activate(w * v, act) : w * activate(v, act);
   }
@@ -188,20 +198,21 @@ moe_rows_kernel(const T *__restrict__ x, long long ldx, const T *__restrict__ up
 }
 
 LLM_EXPORT int llm_moe_rows(int dtype, const void *x, long long ldx, const void *up, const void *down, const int *chosen,
-                            const float *weight, int n_tokens, int top, int width, int ff, int act, int weight_on, float *out,
-                            cudaStream_t stream) {
+                            const float *weight, int n_tokens, int top, int width, int ff, int act, int weight_on, int gated,
+                            float *out, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && top > 0 && width > 0 && ff > 0, "moe_rows: bad sizes");
+  LLM_REQUIRE(!gated || weight_on == 1, "moe_rows: gated experts take their weight on the output");
   const size_t smem = (size_t)(width + ff) * sizeof(float);
   LLM_REQUIRE(smem <= 200 * 1024, "moe_rows: rows of %d + %d values do not fit shared memory", width, ff);
   if (dtype == LLM_F32) {
     LLM_CHECK_CUDA(llm_allow_smem(moe_rows_kernel<float>, smem), "moe_rows attribute");
     llm_launch(moe_rows_kernel<float>, dim3(n_tokens * top), dim3(256), smem, stream, (const float *)x, ldx, (const float *)up,
-               (const float *)down, chosen, weight, n_tokens, top, width, ff, act, weight_on, out);
+               (const float *)down, chosen, weight, n_tokens, top, width, ff, act, weight_on, gated, out);
   } else {
     LLM_CHECK_CUDA(llm_allow_smem(moe_rows_kernel<__nv_bfloat16>, smem), "moe_rows attribute");
     llm_launch(moe_rows_kernel<__nv_bfloat16>, dim3(n_tokens * top), dim3(256), smem, stream, (const __nv_bfloat16 *)x, ldx,
-               (const __nv_bfloat16 *)up, (const __nv_bfloat16 *)down, chosen, weight, n_tokens, top, width, ff, act, weight_on, out);
+               (const __nv_bfloat16 *)up, (const __nv_bfloat16 *)down, chosen, weight, n_tokens, top, width, ff, act, weight_on, gated, out);
   }
   LLM_CHECK_LAUNCH("moe_rows");
   return LLM_OK;
@@ -217,7 +228,7 @@ constexpr int GLD = GK + GPAD;                 // 40 values = 80 bytes a row: ld
 __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const __nv_bfloat16 *__restrict__ A, long long lda, const __nv_bfloat16 *__restrict__ W, int N, int K,
                    const int *__restrict__ offsets, const int *__restrict__ perm, const int *__restrict__ tiles,
-                   const float *__restrict__ weight, int n_tokens, int top, int act, int weight_on, int second,
+                   const float *__restrict__ weight, int n_tokens, int top, int act, int weight_on, int second, int gated,
                    __nv_bfloat16 *__restrict__ mid, float *__restrict__ out) {
   __shared__ __align__(16) __nv_bfloat16 As[GSTAGES][GM][GLD];
   __shared__ __align__(16) __nv_bfloat16 Bs[GSTAGES][GN][GLD];
@@ -306,7 +317,10 @@ moe_grouped_kernel(const __nv_bfloat16 *__restrict__ A, long long lda, const __n
       for (int b = 0; b < 4; ++b) {
         const int n = n0 + wn * 32 + b * 8 + tq * 2;
         const float v0 = acc[a][b][half * 2], v1 = acc[a][b][half * 2 + 1];
-        if (!second) {
+        if (!second && gated) {
+          // columns n (even: the gate's row of feature n / 2) and n + 1 (the up row of the same feature)
+          if (n + 1 < N) mid[(size_t)(place0 + r) * (N / 2) + n / 2] = __float2bfloat16_rn(w * (activate(v0, act) * v1));
+        } else if (!second) {
           __nv_bfloat16 *dst = mid + (size_t)(place0 + r) * N;
           const float y0 = weight_on == 0 ? activate(w * v0, act) : w * activate(v0, act);
           const float y1 = weight_on == 0 ? activate(w * v1, act) : w * activate(v1, act);
@@ -324,20 +338,22 @@ moe_grouped_kernel(const __nv_bfloat16 *__restrict__ A, long long lda, const __n
 // x [tokens, width] bfloat16; mid [tokens * top, ff] bfloat16 scratch; out [top, tokens, width] 32-bit.
 LLM_EXPORT int llm_moe_grouped(const void *x, long long ldx, const void *up, const void *down, const int *offsets, const int *perm,
                                const int *tiles, const float *weight, int n_tokens, int n_experts, int top, int width, int ff,
-                               int act, int weight_on, void *mid, float *out, cudaStream_t stream) {
+                               int act, int weight_on, int gated, void *mid, float *out, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && top > 0 && width > 0 && ff > 0 && n_experts > 0, "moe_grouped: bad sizes");
+  LLM_REQUIRE(!gated || weight_on == 1, "moe_grouped: gated experts take their weight on the output");
   LLM_REQUIRE(width % 8 == 0 && ff % 8 == 0 && ldx % 8 == 0, "moe_grouped: widths %d / %d must be multiples of 8", width, ff);
   LLM_REQUIRE((uintptr_t)x % 16 == 0 && (uintptr_t)up % 16 == 0 && (uintptr_t)down % 16 == 0 && (uintptr_t)mid % 16 == 0,
               "moe_grouped: operands must be 16-byte aligned");
   const int n_rows = n_tokens * top;
   const int max_tiles = min(n_experts, n_rows) + n_rows / GM;
-  llm_launch(moe_grouped_kernel, dim3(max_tiles, (ff + GN - 1) / GN), dim3(256), 0, stream, (const __nv_bfloat16 *)x, ldx,
-             (const __nv_bfloat16 *)up, ff, width, offsets, perm, tiles, weight, n_tokens, top, act, weight_on, 0,
+  const int n_first = gated ? 2 * ff : ff;
+  llm_launch(moe_grouped_kernel, dim3(max_tiles, (n_first + GN - 1) / GN), dim3(256), 0, stream, (const __nv_bfloat16 *)x, ldx,
+             (const __nv_bfloat16 *)up, n_first, width, offsets, perm, tiles, weight, n_tokens, top, act, weight_on, 0, gated,
              (__nv_bfloat16 *)mid, (float *)nullptr);
   LLM_CHECK_LAUNCH("moe_grouped (first product)");
   llm_launch(moe_grouped_kernel, dim3(max_tiles, (width + GN - 1) / GN), dim3(256), 0, stream, (const __nv_bfloat16 *)mid,
-             (long long)ff, (const __nv_bfloat16 *)down, width, ff, offsets, perm, tiles, weight, n_tokens, top, act, weight_on, 1,
+             (long long)ff, (const __nv_bfloat16 *)down, width, ff, offsets, perm, tiles, weight, n_tokens, top, act, weight_on, 1, 0,
              (__nv_bfloat16 *)nullptr, out);
   LLM_CHECK_LAUNCH("moe_grouped (second product)");
   return LLM_OK;
@@ -355,7 +371,7 @@ __global__ void activation_kernel(const TI *__restrict__ in, T *__restrict__ out
 
 LLM_EXPORT int llm_activation(int in_dtype, int dtype, const void *in, void *out, long long n, int act, cudaStream_t stream) {
   if (n == 0) return LLM_OK;
-  LLM_REQUIRE(n > 0 && act >= 0 && act <= 2, "activation: bad arguments");
+  LLM_REQUIRE(n > 0 && act >= 0 && act <= 3, "activation: bad arguments");
   size_t blocks = ((size_t)n + 255) / 256;
   if (blocks > (size_t)sm_count() * 32) blocks = (size_t)sm_count() * 32;
   if (in_dtype == LLM_F32 && dtype == LLM_F32)

@@ -15,6 +15,9 @@
 //                   activation (csrc/moe.cu has the rule) and stores bfloat16 mid[place, ff].
 //   second product  A = mid, W = down [experts, width, ff]; the epilogue scatters 32-bit rows to
 //                   out[choice][token].
+// Gated experts (csrc/moe.cu has the layout: rows of gate and up interleaved, N = 2 ff): a lane of the first
+// epilogue holds one weight row, so neighbouring lanes hold a feature's gate and up values for the same token;
+// the even lane takes its neighbour's by a shuffle and stores weight * act(gate) * up to mid[place, feature].
 // A box of sorted rows may reach into the next expert's rows, and a box of weight rows into the next
 // expert's: such products are computed and never stored.  Every wait has a time limit, after which
 // the CTA records a code in `status`, lets its loads land, frees its tensor memory and returns.
@@ -34,6 +37,7 @@ template <int KIND>
 __device__ __forceinline__ float mt_activate(float z) {
   if (KIND == 0) return 0.5f * z * (1.f + erff(z * 0.70710678118654752f));
   if (KIND == 1) return 0.5f * z * (1.f + tanhf(0.79788456080286536f * (z + 0.044715f * z * z * z)));
+  if (KIND == 3) return z > 0.f ? z * z : 0.f;
   return z / (1.f + expf(-z));
 }
 
@@ -50,7 +54,7 @@ struct MtShape {
 // ACT: the activation of the first product (csrc/moe.cu numbers them), or -1 for the second product.  The kind of
 // product and the activation are the compiler's to know: with them as arguments the epilogue's loop was
 // branches around every element, and the sixteen values of a load were worked through one after the other.
-template <int TN, int ACT>
+template <int TN, int ACT, bool GATED>
 __global__ void __launch_bounds__(MT_THREADS, 1)
 moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, int N, int K,
               const int *__restrict__ offsets, const int *__restrict__ perm, const int *__restrict__ tiles,
@@ -206,6 +210,10 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
           for (int i = 0; i < 16; ++i) {
             if (SECOND) {
               y[i] = v[i];
+            } else if (GATED) {
+              const float w = __shfl_sync(0xffffffffu, my_w[c0 >> 5], (c0 & 31) + i);
+              const float other = __shfl_xor_sync(0xffffffffu, v[i], 1);     // the odd lane's value: the up row
+              y[i] = w * (mt_activate<SECOND ? 0 : ACT>(v[i]) * other);
             } else {
               const float w = __shfl_sync(0xffffffffu, my_w[c0 >> 5], (c0 & 31) + i);
               const float a = mt_activate<SECOND ? 0 : ACT>(weight_on == 0 ? w * v[i] : v[i]);
@@ -217,7 +225,8 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
             const int row = __shfl_sync(0xffffffffu, my_row[c0 >> 5], (c0 & 31) + i);
             if (c0 + i < count && f < N) {
               if (SECOND) out[(size_t)row * N + f] = y[i];
-              else mid[(size_t)row * N + f] = __float2bfloat16_rn(y[i]);
+              else if (!GATED) mid[(size_t)row * N + f] = __float2bfloat16_rn(y[i]);
+              else if ((lane & 1) == 0) mid[(size_t)row * (N / 2) + f / 2] = __float2bfloat16_rn(y[i]);
             }
           }
         }
@@ -239,7 +248,7 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
   }
 }
 
-template <int TN, int ACT>
+template <int TN, int ACT, bool GATED>
 int launch_moe_tc(const void *a, long long n_rows, const void *w, int n_experts, int N, int K, const int *offsets,
                   const int *perm, const int *tiles, const float *weight, int n_tokens, int top, int weight_on, void *mid,
                   float *out, int *status, cudaStream_t stream) {
@@ -249,7 +258,7 @@ int launch_moe_tc(const void *a, long long n_rows, const void *w, int n_experts,
   if (rc != LLM_OK) return rc;
   rc = get_map(a, n_rows, K, K, TN, &map_x);
   if (rc != LLM_OK) return rc;
-  auto kern = moe_tc_kernel<TN, ACT>;
+  auto kern = moe_tc_kernel<TN, ACT, GATED>;
   LLM_CHECK_CUDA(llm_allow_smem(kern, S::SMEM), "moe_tc attribute");
   const long long most = ((long long)(n_experts < n_rows ? n_experts : n_rows) + n_rows / TN) * ((N + MT_ROWS - 1) / MT_ROWS);
   const int grid = (int)(most < sm_count() ? most : sm_count());
@@ -270,27 +279,30 @@ LLM_EXPORT int llm_moe_tc_supports(int width, int ff) { return width % 8 == 0 &&
 // `tiles` must have been made with tiles of llm_moe_tc_tile_rows(tokens * top) rows.
 LLM_EXPORT int llm_moe_tc(const void *xs, const void *up, const void *down, const int *offsets, const int *perm,
                           const int *tiles, const float *weight, int n_tokens, int n_experts, int top, int width, int ff,
-                          int act, int weight_on, void *mid, float *out, int *status, cudaStream_t stream) {
+                          int act, int weight_on, int gated, void *mid, float *out, int *status, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(!gated || weight_on == 1, "moe_tc: gated experts take their weight on the output");
   LLM_REQUIRE(n_tokens > 0 && top > 0 && width > 0 && ff > 0 && n_experts > 0, "moe_tc: bad sizes");
   LLM_REQUIRE(llm_moe_tc_supports(width, ff), "moe_tc: widths %d / %d must be multiples of 8", width, ff);
   LLM_REQUIRE((uintptr_t)xs % 16 == 0 && (uintptr_t)up % 16 == 0 && (uintptr_t)down % 16 == 0 && (uintptr_t)mid % 16 == 0,
               "moe_tc: operands must be 16-byte aligned");
-  LLM_REQUIRE((long long)n_experts * (ff > width ? ff : width) < (1ll << 31), "moe_tc: the stacked weights have too many rows");
-  LLM_REQUIRE(act >= 0 && act <= 2, "moe_tc: unknown activation %d", act);
+  LLM_REQUIRE((long long)n_experts * (2 * ff > width ? 2 * ff : width) < (1ll << 31), "moe_tc: the stacked weights have too many rows");
+  LLM_REQUIRE(act >= 0 && act <= 3, "moe_tc: unknown activation %d", act);
   const long long n_rows = (long long)n_tokens * top;
-#define MT_FIRST(TN, ACT)                                                                                                    \
-  launch_moe_tc<TN, ACT>(xs, n_rows, up, n_experts, ff, width, offsets, perm, tiles, weight, n_tokens, top, weight_on, mid, nullptr, \
-                         status, stream)
+#define MT_FIRST(TN, ACT, GATED)                                                                                             \
+  launch_moe_tc<TN, ACT, GATED>(xs, n_rows, up, n_experts, GATED ? 2 * ff : ff, width, offsets, perm, tiles, weight, n_tokens, top, \
+                                weight_on, mid, nullptr, status, stream)
+#define MT_ACTS(TN, GATED) (act == 0 ? MT_FIRST(TN, 0, GATED) : act == 1 ? MT_FIRST(TN, 1, GATED) : act == 2 ? MT_FIRST(TN, 2, GATED) : MT_FIRST(TN, 3, GATED))
 #define MT_BOTH(TN)                                                                                                          \
   do {                                                                                                                       \
-    const int rc = act == 0 ? MT_FIRST(TN, 0) : act == 1 ? MT_FIRST(TN, 1) : MT_FIRST(TN, 2);                                \
+    const int rc = gated ? MT_ACTS(TN, true) : MT_ACTS(TN, false);                                                           \
     if (rc != LLM_OK) return rc;                                                                                             \
-    return launch_moe_tc<TN, -1>(mid, n_rows, down, n_experts, width, ff, offsets, perm, tiles, weight, n_tokens, top, weight_on, \
-                                 nullptr, out, status, stream);                                                              \
+    return launch_moe_tc<TN, -1, false>(mid, n_rows, down, n_experts, width, ff, offsets, perm, tiles, weight, n_tokens, top, \
+                                        weight_on, nullptr, out, status, stream);                                            \
   } while (0)
   if (llm_moe_tc_tile_rows((int)n_rows) == 32) MT_BOTH(32);
   MT_BOTH(128);
 #undef MT_BOTH
+#undef MT_ACTS
 #undef MT_FIRST
 }

@@ -193,10 +193,11 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, 
                       tok_seq: torch.Tensor, tok_pos: torch.Tensor, page_table: torch.Tensor,
                       n_heads: int, n_kv: int, head_dim: int, page_size: int, window: Optional[int],
                       scale: float, v_head_dim: Optional[int] = None, block: Optional[int] = None,
-                      gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      gate: Optional[torch.Tensor] = None, sink: int = 0) -> torch.Tensor:
     """q is a [T, >= n_heads*d] view whose first n_heads*d columns are the rotated queries.  Values
     may have a width of their own; ``block``: a query sees only the keys of its own block of that
-    many positions; ``gate`` [T, >= n_heads] 32-bit: head results are multiplied by sigmoid(gate)."""
+    many positions; ``sink``: with a window, the first positions that stay visible; ``gate``
+    [T, >= n_heads] 32-bit: head results are multiplied by sigmoid(gate)."""
     _on_gpu(q, out, kcache, vcache, tok_seq, tok_pos, page_table, gate)
     T = q.shape[0]
     dv = int(v_head_dim or head_dim)
@@ -206,10 +207,10 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, 
         assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == T
     _call("attention_generic", "llm_attention_generic",
           [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
-           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_longlong, c_void_p],
+           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_longlong, c_void_p],
           dtype_code(q.dtype), _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache),
           _ptr(tok_seq), _ptr(tok_pos), _ptr(page_table), page_table.stride(0), T, n_heads, n_kv, head_dim, dv,
-          page_size, int(window or 0), int(block or 0), float(scale), _ptr(gate), gate.stride(0) if gate is not None else 0,
+          page_size, int(window or 0), int(block or 0), int(sink or 0), float(scale), _ptr(gate), gate.stride(0) if gate is not None else 0,
           _stream())
     return out
 
@@ -250,7 +251,7 @@ def concat_stream(resid: torch.Tensor, delta: Optional[torch.Tensor], other: tor
 
 
 # ------------------------------------------------------------------ routed feed-forward
-ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2}
+ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1, "silu": 2, "relu2": 3}
 
 
 def moe_route(logits: torch.Tensor, top: int, score: str = "sigmoid", renormalize: bool = False):
@@ -267,22 +268,23 @@ def moe_route(logits: torch.Tensor, top: int, score: str = "sigmoid", renormaliz
 
 
 def moe_experts(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor, weight: torch.Tensor,
-                act: str = "gelu", weight_on: str = "input", grouped: bool = False) -> torch.Tensor:
+                act: str = "gelu", weight_on: str = "input", grouped: bool = False, gated: bool = False) -> torch.Tensor:
     """out [top, T, width] 32-bit: the chosen experts' down(act(up(x))), a row per choice.  up [E, ff, width],
-    down [E, width, ff].  ``grouped``: rows sorted by expert and multiplied on the tensor cores (bfloat16), True with
+    down [E, width, ff].  ``gated``: up is [E, 2 ff, width], an expert's gate and up rows interleaved (row 2n the gate's),
+    and the expert is down(act(gate x) * up x), weighted on its output.  ``grouped``: rows sorted by expert and multiplied on the tensor cores (bfloat16), True with
     mma.sync, "tc" with tcgen05."""
     _on_gpu(x, up, down, chosen, weight)
     T, width = x.shape
-    E, ff = up.shape[0], up.shape[1]
+    E, ff = up.shape[0], up.shape[1] // (2 if gated else 1)
     top = chosen.shape[1]
     assert up.is_contiguous() and down.is_contiguous() and x.stride(1) == 1 and up.dtype == x.dtype == down.dtype
     assert tuple(down.shape) == (E, width, ff) and chosen.is_contiguous() and weight.is_contiguous()
     out = torch.empty(top, T, width, dtype=torch.float32, device=x.device)
     if not grouped:
         _call("moe", "llm_moe_rows", [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                      c_int, c_int, c_int, c_void_p, c_void_p],
+                                      c_int, c_int, c_int, c_int, c_void_p, c_void_p],
               dtype_code(x.dtype), _ptr(x), x.stride(0), _ptr(up), _ptr(down), _ptr(chosen), _ptr(weight), T, top, width, ff,
-              ACTIVATIONS[act], 1 if weight_on == "output" else 0, _ptr(out), _stream())
+              ACTIVATIONS[act], 1 if weight_on == "output" else 0, int(gated), _ptr(out), _stream())
         return out
     assert x.dtype == torch.bfloat16
     n_rows = T * top
@@ -305,14 +307,14 @@ def moe_experts(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, chosen: t
         _call("moe", "llm_moe_gather", [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
               _ptr(x), x.stride(0), _ptr(perm), n_rows, top, width, _ptr(xs), _stream())
         _call("moe_tc", "llm_moe_tc", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                       c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+                                       c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
               _ptr(xs), _ptr(up), _ptr(down), _ptr(offsets), _ptr(perm), _ptr(tiles), _ptr(weight), T, E, top, width, ff,
-              ACTIVATIONS[act], 1 if weight_on == "output" else 0, _ptr(mid), _ptr(out), _ptr(tc_status(x.device)), _stream())
+              ACTIVATIONS[act], 1 if weight_on == "output" else 0, int(gated), _ptr(mid), _ptr(out), _ptr(tc_status(x.device)), _stream())
         return out
     _call("moe", "llm_moe_grouped", [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                     c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
           _ptr(x), x.stride(0), _ptr(up), _ptr(down), _ptr(offsets), _ptr(perm), _ptr(tiles), _ptr(weight), T, E, top, width,
-          ff, ACTIVATIONS[act], 1 if weight_on == "output" else 0, _ptr(mid), _ptr(out), _stream())
+          ff, ACTIVATIONS[act], 1 if weight_on == "output" else 0, int(gated), _ptr(mid), _ptr(out), _stream())
     return out
 
 

@@ -372,3 +372,70 @@ LLM_EXPORT int llm_qk_place(int in_dtype, int dtype, const void *qkv, long long 
   LLM_CHECK_LAUNCH("qk_place");
   return LLM_OK;
 }
+
+// ---------------------------------------------------------------- placing without rotation: bias, value norm
+// Rows [q | k | v (n_kv * dv) | ...] of a stacked product whose matrix has biases and whose
+// attention uses no rotation: the bias (32-bit, one value per stacked row of the matrix; null:
+// none) is added here, in 32-bit, so that the product itself can run without one; each value head
+// is divided by its root mean square over dv, sqrt(mean(v^2) + v_eps), when v_eps >= 0 (no
+// weight), and is cached so.  q goes to q_out, k and v to the cache.  A CTA a token; a warp takes
+// a value head at a time (sum in lane order, then the shuffle tree).
+template <typename TI, typename T>
+__global__ void __launch_bounds__(256)
+kv_place_kernel(const TI *__restrict__ qkv, long long row_stride, T *__restrict__ q_out, long long q_stride, int n_heads,
+                int n_kv, int d, int dv, const float *__restrict__ bias, float v_eps, const int *__restrict__ tok_seq,
+                const int *__restrict__ tok_pos, const int *__restrict__ page_table, int pt_stride, T *__restrict__ kcache,
+                T *__restrict__ vcache, int page_size, int write_cache) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  const int t = blockIdx.x;
+  const TI *row = qkv + (size_t)t * row_stride;
+  const int qw = n_heads * d, kw = n_kv * d;
+  for (int c = threadIdx.x; c < qw; c += 256)
+    q_out[(size_t)t * q_stride + c] = from_float<T>(to_float(row[c]) + (bias ? bias[c] : 0.f));
+  if (!write_cache) return;
+  const int pos = tok_pos[t];
+  const int page = page_table[(size_t)tok_seq[t] * pt_stride + pos / page_size];
+  const size_t cache_row = (size_t)page * n_kv * page_size + (pos % page_size);
+  for (int c = threadIdx.x; c < kw; c += 256) {
+    const int kvh = c / d, ch = c - kvh * d;
+    kcache[(cache_row + (size_t)kvh * page_size) * d + ch] = from_float<T>(to_float(row[qw + c]) + (bias ? bias[qw + c] : 0.f));
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int kvh = warp; kvh < n_kv; kvh += 8) {
+    const TI *v = row + qw + kw + (size_t)kvh * dv;
+    const float *vb = bias ? bias + qw + kw + (size_t)kvh * dv : nullptr;
+    float inv = 1.f;
+    if (v_eps >= 0.f) {
+      float ss = 0.f;
+      for (int i = lane; i < dv; i += 32) {
+        const float x = to_float(v[i]) + (vb ? vb[i] : 0.f);
+        ss = fmaf(x, x, ss);
+      }
+      ss = warp_sum(ss);
+      inv = 1.f / sqrtf(ss / (float)dv + v_eps);
+    }
+    T *dst = vcache + (cache_row + (size_t)kvh * page_size) * dv;
+    for (int i = lane; i < dv; i += 32) dst[i] = from_float<T>((to_float(v[i]) + (vb ? vb[i] : 0.f)) * inv);
+  }
+}
+
+LLM_EXPORT int llm_kv_place(int in_dtype, int dtype, const void *qkv, long long row_stride, void *q_out, long long q_stride,
+                            int n_tokens, int n_heads, int n_kv, int d, int dv, const float *bias, float v_eps,
+                            const int *tok_seq, const int *tok_pos, const int *page_table, int pt_stride, void *kcache,
+                            void *vcache, int page_size, int write_cache, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && d > 0 && dv > 0, "kv_place: bad sizes");
+  LLM_REQUIRE(row_stride >= (long long)n_heads * d + (long long)n_kv * (d + dv), "kv_place: the stacked rows are too short");
+#define KV_PLACE(TI, T)                                                                                                  \
+  llm_launch(kv_place_kernel<TI, T>, dim3(n_tokens), dim3(256), 0, stream, (const TI *)qkv, row_stride, (T *)q_out, q_stride, \
+             n_heads, n_kv, d, dv, bias, v_eps, tok_seq, tok_pos, page_table, pt_stride, (T *)kcache, (T *)vcache, page_size, \
+             write_cache)
+  if (in_dtype == LLM_F32 && dtype == LLM_F32) KV_PLACE(float, float);
+  else if (in_dtype == LLM_F32 && dtype == LLM_BF16) KV_PLACE(float, __nv_bfloat16);
+  else if (in_dtype == LLM_BF16 && dtype == LLM_BF16) KV_PLACE(__nv_bfloat16, __nv_bfloat16);
+  else LLM_FAIL("kv_place: unsupported dtypes in %d out %d", in_dtype, dtype);
+#undef KV_PLACE
+  LLM_CHECK_LAUNCH("kv_place");
+  return LLM_OK;
+}

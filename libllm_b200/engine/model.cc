@@ -36,6 +36,7 @@ class StateMapLoader : public Loader {
   StateMapLoader(const StateMap &s, DType engine) : Loader(engine), state_(s) {}
   void fetch_into(const TensorNeed &need, DType target, void *dst) const override { state_.fetch_into(need, target, dst); }
   bool has(const std::string &name) const override { return state_.has(name); }
+  std::vector<int64_t> shape_of(const std::string &name) const override { return state_.stored(name).shape; }
 
  private:
   const StateMap &state_;
@@ -83,6 +84,7 @@ Model::Model(ModelSpec spec, Json config, DType dtype, int64_t max_positions, in
 std::vector<TensorNeed> Model::tensor_needs() const {
   std::vector<TensorNeed> needs;
   needs.push_back({spec_.embedding, {spec_.vocab_size, spec_.hidden}});
+  if (!spec_.position_table.empty()) needs.push_back({spec_.position_table, {spec_.max_positions, spec_.hidden}});
   for (const auto &l : layers_)
     for (auto &n : l->tensor_needs()) needs.push_back(n);
   for (auto &n : final_norm_->tensor_needs()) needs.push_back(n);
@@ -109,6 +111,7 @@ bool Model::capturable() const {
 void Model::load_with(const Loader &loader) {
   const std::vector<TensorNeed> needs = tensor_needs();
   embedding_ = loader.fetch(needs.front());
+  if (!spec_.position_table.empty()) positions_ = loader.fetch(needs[1]);
   for (auto &l : layers_) l->load(loader);
   final_norm_->load(loader);
   for (auto &kv : input_mixes_) kv.second = loader.fetch({kv.first, {spec_.hidden, 2 * spec_.hidden}});
@@ -149,10 +152,7 @@ void Model::cache_needs(std::vector<CacheNeed> *needs, std::vector<char> *has) c
 
 std::vector<std::vector<StateNeed>> Model::state_needs() const {
   std::vector<std::vector<StateNeed>> out;
-  for (const auto &e : spec_.schedule) {
-    Mixer *m = layers_[(size_t)e.layer]->mixer_part();
-    out.push_back(m ? m->state_need() : std::vector<StateNeed>());
-  }
+  for (const auto &e : spec_.schedule) out.push_back(layers_[(size_t)e.layer]->state_need());
   return out;
 }
 
@@ -179,7 +179,7 @@ Act Model::forward(StepContext &ctx, KVCache &cache, const std::vector<const int
   const int64_t T = ctx.n_tokens, H = spec_.hidden;
   float *resid = ctx.arena->alloc_n<float>((size_t)(T * H));
   kernels::embedding(embedding_.dtype, embedding_.data(), ctx.tokens, fed_tokens, fed_rows, resid, (int)T, (int)H,
-                     (int)spec_.vocab_size, ctx.stream);
+                     (int)spec_.vocab_size, ctx.stream, positions_.data(), (int)positions_.rows, ctx.tok_pos);
   if (spec_.embedding_scale != 1.0) kernels::scale_rows(resid, T * H, (float)spec_.embedding_scale, ctx.stream);
   float *x0 = nullptr;                       // the token rows, kept for the runs that mix them in again
   if (!input_mixes_.empty()) {
@@ -272,8 +272,10 @@ void create_random_model(const std::string &folder, const Json &config_json, uin
   std::vector<NamedTensor> tensors;
   std::vector<std::vector<uint8_t>> storage;
   std::vector<float> values;
-  for (const auto &need : model->tensor_needs()) {
+  for (TensorNeed need : model->tensor_needs()) {
     if (need.optional) continue;
+    for (auto &size : need.shape)
+      if (size < 0) size = DRAWN_FREE_SIZE;
     random_tensor_host(need, seed, &values);
     NamedTensor nt;
     nt.name = need.name;

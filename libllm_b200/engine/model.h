@@ -66,7 +66,7 @@ class Model {
   std::map<std::string, std::shared_ptr<Weight>> shared_;
   std::vector<std::unique_ptr<Block>> layers_;
   std::unique_ptr<Norm> final_norm_;
-  Weight embedding_, head_own_;
+  Weight embedding_, head_own_, positions_;        // positions_: ModelSpec::position_table, in the token table's type
   std::map<std::string, Weight> input_mixes_;      // ScheduleEntry::input_mix -> [hidden, 2 * hidden]
   void mix_input(StepContext &ctx, ResidualStream &stream, const float *x0, const Weight &w);
   const Weight *head_ = nullptr;

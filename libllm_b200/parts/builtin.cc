@@ -53,6 +53,47 @@ class RMSNorm : public Norm {
   Weight weight_;
 };
 
+// ---------------------------------------------------------------- layer norm
+// y = (x - mean) / sqrt(var + eps) * w + b, var the mean of the squared deviations, everything in
+// 32-bit; `bias` may be left out.  The stream's pending addition is applied first, as in RMSNorm.
+class LayerNorm : public Norm {
+ public:
+  LayerNorm(const Json &spec, const BuildEnv &env) : Norm(spec, env) {
+    ConfigReader r = reader_of(spec, "layernorm");
+    size_ = r.integer("size");
+    eps_ = r.number("eps");
+    name_ = r.string("weight");
+    bias_name_ = r.string_or("bias", "");
+  }
+  std::vector<TensorNeed> tensor_needs() const override {
+    std::vector<TensorNeed> needs = {{name_, {size_}, TensorRole::Vector, false}};
+    if (!bias_name_.empty()) needs.push_back({bias_name_, {size_}, TensorRole::Vector, false});
+    return needs;
+  }
+  void load(const Loader &l) override {
+    const auto needs = tensor_needs();
+    weight_ = l.fetch(needs[0]);
+    if (needs.size() > 1) bias_ = l.fetch(needs[1]);
+  }
+  std::vector<std::string> kernel_families() const override { return {"elementwise"}; }
+  Act forward(StepContext &ctx, ResidualStream &stream, const int *rows, int n_rows) override {
+    const int64_t n = rows ? n_rows : stream.rows;
+    Act out = ctx.arena->act(ctx.dtype, n, size_);
+    flush_chain(ctx);
+    kernels::add_layernorm(stream.resid, stream.pending.data ? &stream.pending : nullptr, weight_.buf.as<float>(),
+                           bias_name_.empty() ? nullptr : bias_.buf.as<float>(), (float)eps_, out.data, ctx.dtype, rows, (int)n,
+                           (int)size_, ctx.stream);
+    if (!rows) stream.pending = Act();
+    return out;
+  }
+
+ private:
+  int64_t size_;
+  double eps_;
+  std::string name_, bias_name_;
+  Weight weight_, bias_;
+};
+
 // ---------------------------------------------------------------- rotary position encoding
 // f_i = theta^(-2i/d) for i < d/2.  With llama3 scaling a frequency whose wavelength 2*pi/f is
 // shorter than original/high_freq_factor is kept, one longer than original/low_freq_factor is
@@ -160,6 +201,14 @@ class RotaryEmbedding : public PositionEncoding {
 //                position 0 of the sequence (a chunked mask); the cache gives earlier pages back
 //   head_gate    a matrix [n_heads, hidden]: head h's result is multiplied by sigmoid(gate x)_h
 //                before the output projection; its rows ride at the end of the stacked product
+//   out_gate     a matrix [n_heads * v_head_dim, hidden]: the same per channel of the concatenated heads
+//   sink         with `window`: the first `sink` positions of a sequence stay visible to every later query
+//                (at their true positions); the cache holds on to their pages
+//   v_norm       {eps}: every value head is divided by its root mean square over its channels before it
+//                is cached (no weight)
+//   q_bias, k_bias, v_bias   names of the biases (default: the matrix's name with "weight" replaced by "bias").
+//                Without a rotation the biases are added where q, k and v are placed (32-bit), so that the
+//                product itself runs on the tensor cores like any other
 class Attention : public Mixer {
  public:
   Attention(const Json &spec, const BuildEnv &env) : Mixer(spec, env) {
@@ -186,16 +235,29 @@ class Attention : public Mixer {
       qk_eps_ = (float)n.number("eps");
     }
     gate_name_ = r.string_or("head_gate", "");
-    if (bias_ && (!gate_name_.empty() || !q_norm_name_.empty()))
-      LLM_THROW(Unsupported, "attention: a bias together with a head gate or a q/k norm is not built");
+    const std::string out_gate = r.string_or("out_gate", "");
+    if (!out_gate.empty()) {
+      if (!gate_name_.empty()) LLM_THROW(Config, "attention: a gate per head or per channel, not both");
+      gate_name_ = out_gate;
+      gate_per_channel_ = true;
+    }
+    sink_ = (int)r.integer_or("sink", 0, 0);
+    if (sink_ > 0 && (window_ == 0 || block_ > 0)) LLM_THROW(Config, "attention: kept first positions ('sink') go with a window");
+    if (r.present("v_norm")) v_eps_ = (float)ConfigReader(r.object("v_norm"), "attention description: v_norm").number("eps", false);
     if (!spec.get("position").is_null()) position_ = build_as<PositionEncoding>("position", spec.get("position"), env);
+    place_adds_bias_ = !position_ && q_norm_name_.empty();
+    if (v_eps_ >= 0.f && !place_adds_bias_) LLM_THROW(Unsupported, "attention: a value norm together with a rotation or a q/k norm is not built");
+    if (bias_ && !place_adds_bias_ && (!gate_name_.empty() || !q_norm_name_.empty()))
+      LLM_THROW(Unsupported, "attention: a bias together with a rotation and a gate or a q/k norm is not built");
+    for (const char *key : {"q_bias", "k_bias", "v_bias"}) bias_names_.push_back(r.string_or(key, ""));
     q_width_ = (int64_t)n_heads_ * d_;
     kv_width_ = (int64_t)n_kv_ * d_;
     v_width_ = (int64_t)n_kv_ * dv_;
     o_width_ = (int64_t)n_heads_ * dv_;
     gate_offset_ = q_width_ + kv_width_ + v_width_;
     // rows of the stacked matrix: a multiple of 8, so that rows of the 32-bit product start on 32 bytes
-    stacked_rows_ = (gate_offset_ + (gate_name_.empty() ? 0 : n_heads_) + 7) / 8 * 8;
+    gate_rows_ = gate_name_.empty() ? 0 : gate_per_channel_ ? o_width_ : (int64_t)n_heads_;
+    stacked_rows_ = (gate_offset_ + gate_rows_ + 7) / 8 * 8;
     // the tiled attention kernels take heads whose values are as wide as their keys, in multiples of 16
     plain_ = dv_ == d_ && d_ % 16 == 0 && d_ >= 16 && scale_ > 0.f;
   }
@@ -203,18 +265,22 @@ class Attention : public Mixer {
   std::vector<TensorNeed> tensor_needs() const override {
     std::vector<TensorNeed> needs = {{q_name_, {q_width_, hidden_}}, {k_name_, {kv_width_, hidden_}}, {v_name_, {v_width_, hidden_}},
                                      {o_name_, {hidden_, o_width_}}};
-    if (bias_)
-      for (const auto &p : {std::make_pair(q_name_, q_width_), std::make_pair(k_name_, kv_width_), std::make_pair(v_name_, kv_width_)}) {
+    if (bias_) {
+      size_t which = 0;
+      for (const auto &p : {std::make_pair(q_name_, q_width_), std::make_pair(k_name_, kv_width_), std::make_pair(v_name_, v_width_)}) {
         std::string n = p.first;
         const std::string suffix = "weight";
         if (n.size() >= suffix.size() && n.compare(n.size() - suffix.size(), suffix.size(), suffix) == 0) n.resize(n.size() - suffix.size());
-        needs.push_back({n + "bias", {p.second}, TensorRole::Vector, false});
+        const std::string given = which < bias_names_.size() ? bias_names_[which] : "";
+        needs.push_back({given.empty() ? n + "bias" : given, {p.second}, TensorRole::Vector, false});
+        ++which;
       }
+    }
     if (!q_norm_name_.empty()) {
       needs.push_back({q_norm_name_, {q_width_}, TensorRole::Vector, false});
       needs.push_back({k_norm_name_, {kv_width_}, TensorRole::Vector, false});
     }
-    if (!gate_name_.empty()) needs.push_back({gate_name_, {(int64_t)n_heads_, hidden_}});
+    if (!gate_name_.empty()) needs.push_back({gate_name_, {gate_rows_, hidden_}});
     if (position_)
       for (auto &n : position_->tensor_needs()) needs.push_back(n);
     return needs;
@@ -248,7 +314,7 @@ class Attention : public Mixer {
       l.fetch_into(needs[4], DType::F32, b);
       l.fetch_into(needs[5], DType::F32, b + q_width_);
       l.fetch_into(needs[6], DType::F32, b + q_width_ + kv_width_);
-      if (l.engine == DType::BF16) {
+      if (l.engine == DType::BF16 && !place_adds_bias_) {
         static bool said = false;
         if (!said) {
           said = true;
@@ -270,6 +336,7 @@ class Attention : public Mixer {
     if (!plain_) return fams;
     if (!gate_name_.empty()) fams.push_back("elementwise");
     const bool tiled = env_.page_size == 64 && d_ % 16 == 0 && d_ >= 16 && d_ <= 128;
+    if (sink_ > 0) return fams;          // kept first positions: the general kernel
     if (f.prefill_attention_tc && env_.page_size == 64 && (d_ == 64 || d_ == 128)) fams.push_back("attention_prefill_tc");
     else if (f.prefill_attention && tiled) fams.push_back("attention_prefill");
     if (f.decode_attention_tc && tiled && group <= 16 && !bias_ && position_ && gate_name_.empty() && q_norm_name_.empty())
@@ -290,6 +357,7 @@ class Attention : public Mixer {
     n.v_dim = dv_;
     n.window = n.kind == "window" ? window_ : 0;
     n.block = n.kind == "block" ? block_ : 0;
+    n.sink = n.kind == "window" ? sink_ : 0;
     return n;
   }
 
@@ -305,7 +373,7 @@ class Attention : public Mixer {
     const float *gate = nullptr;
     const bool fused = plain_ && !has_gate && q_norm_name_.empty() && table && !bias_ && ctx.decode_only && f.decode_attention_tc && ctx.dtype == DType::BF16 &&
                        kernels::available("attention_decode_tc") && kernels::attention_decode_tc_supported(d_, cache->page_size, group);
-    Act qkv = linear(ctx, x, w_qkv_, bias_ ? b_qkv_.buf.as<float>() : nullptr, DType::F32, fused);
+    Act qkv = linear(ctx, x, w_qkv_, bias_ && !place_adds_bias_ ? b_qkv_.buf.as<float>() : nullptr, DType::F32, fused);
     flush_chain(ctx);
     if (fused) {
       const int max_len = std::max(ctx.max_kv_len, 1);
@@ -334,7 +402,10 @@ class Attention : public Mixer {
     Act q = ctx.arena->act(ctx.dtype, ctx.n_tokens, q_width_);
     const QkvLayout layout{n_heads_, n_kv_, d_};
     if (has_gate) gate = (const float *)qkv.data + gate_offset_;
-    if (!q_norm_name_.empty() || dv_ != d_) {
+    if (place_adds_bias_ && (bias_ || v_eps_ >= 0.f)) {
+      kernels::kv_place(qkv, q, n_heads_, n_kv_, d_, dv_, bias_ ? b_qkv_.buf.as<float>() : nullptr, v_eps_, ctx.tok_seq, ctx.tok_pos,
+                        cache->page_table, cache->table_width, cache->k, cache->v, cache->page_size, cache->writes, ctx.stream);
+    } else if (!q_norm_name_.empty() || dv_ != d_) {
       if (position_ && !table)
         LLM_THROW(Unsupported, "attention: a q/k norm or values of another width need a position part with a half-split table (or none)");
       kernels::qk_place(qkv, q, n_heads_, n_kv_, d_, dv_, q_norm_.buf.as<float>(), k_norm_.buf.as<float>(), qk_eps_, table, table_rows,
@@ -348,7 +419,10 @@ class Attention : public Mixer {
     }
     Act out = ctx.arena->act(ctx.dtype, ctx.n_tokens, o_width_);
     bool done = false;
-    if (ctx.dtype == DType::BF16 && plain_) {
+    // a gate per channel is applied behind the attention kernel, whichever it is
+    const float *channel_gate = gate_per_channel_ ? gate : nullptr;
+    if (gate_per_channel_) gate = nullptr;
+    if (ctx.dtype == DType::BF16 && plain_ && sink_ == 0) {
       if (ctx.decode_only && f.decode_attention && kernels::available("attention_decode") &&
           kernels::attention_decode_supported(d_, group)) {
         // enough CTAs to fill the GPU about eight times over at the longest length, runs of at
@@ -387,15 +461,18 @@ class Attention : public Mixer {
     }
     if (!done)
       kernels::attention_generic(q, out, cache->k, cache->v, ctx.tok_seq, ctx.tok_pos, cache->page_table, cache->table_width,
-                                 n_heads_, n_kv_, d_, dv_, cache->page_size, window_, block_, scale_, gate, qkv.ld, ctx.stream);
+                                 n_heads_, n_kv_, d_, dv_, cache->page_size, window_, block_, scale_, gate, qkv.ld, ctx.stream, sink_);
+    if (channel_gate) kernels::head_gate(out, channel_gate, qkv.ld, n_heads_ * dv_, 1, ctx.stream);
     return linear(ctx, out, w_o_, nullptr, DType::F32, true);
   }
 
  private:
   int64_t hidden_, q_width_, kv_width_, v_width_, o_width_, gate_offset_, stacked_rows_;
-  int n_heads_, n_kv_, d_, dv_, window_, block_;
-  bool bias_, plain_;
-  float scale_, qk_eps_ = 0.f;
+  int64_t gate_rows_ = 0;
+  int n_heads_, n_kv_, d_, dv_, window_, block_, sink_ = 0;
+  bool bias_, plain_, gate_per_channel_ = false, place_adds_bias_ = false;
+  float scale_, qk_eps_ = 0.f, v_eps_ = -1.f;
+  std::vector<std::string> bias_names_;
   std::string q_name_, k_name_, v_name_, o_name_, q_norm_name_, k_norm_name_, gate_name_;
   std::unique_ptr<PositionEncoding> position_;
   Weight w_qkv_, w_o_, b_qkv_, q_norm_, k_norm_;
@@ -466,31 +543,62 @@ class SwiGLU : public FeedForward {
 
 // ---------------------------------------------------------------- pre-norm block
 // h = x + mixer(norm1(x)); out = h + ff(norm2(h)) (src/libllm/llama.cc:251-267).  Each addition is
-// left pending on the stream and applied, in 32-bit, by the next norm.
+// left pending on the stream and applied, in 32-bit, by the next norm.  Options:
+//   mixer_conv  {taps, weight}: what the mixer reads, n = norm1(x), becomes n + conv(n), a causal
+//               convolution over time on each channel (weight [hidden, taps], the last tap on the
+//               token itself, zeros before the sequence's start); the last taps - 1 rows of n are
+//               state of the run, per sequence, in the engine's type
+//   ff, ff_norm may be null: the block is the mixer alone
+const char *const CONV_STATE = "mixer_conv.inputs";
 class PreNormBlock : public Block {
  public:
   PreNormBlock(const Json &spec, const BuildEnv &env) : Block(spec, env) {
     ConfigReader r = reader_of(spec, "prenorm block");
     mixer_norm_ = build_as<Norm>("norm", r.object("mixer_norm"), env);
     mixer_ = build_as<Mixer>("mixer", r.object("mixer"), env);
-    ff_norm_ = build_as<Norm>("norm", r.object("ff_norm"), env);
-    ff_ = build_as<FeedForward>("feed_forward", r.object("ff"), env);
+    if (r.present("ff")) {
+      ff_norm_ = build_as<Norm>("norm", r.object("ff_norm"), env);
+      ff_ = build_as<FeedForward>("feed_forward", r.object("ff"), env);
+    }
+    if (r.present("mixer_conv")) {
+      ConfigReader c(r.object("mixer_conv"), "prenorm block: mixer_conv");
+      taps_ = (int)c.integer("taps");
+      conv_name_ = c.string("weight");
+      hidden_ = c.integer("hidden");
+      if (taps_ > 8) LLM_THROW(Unsupported, "prenorm block: a convolution of %d taps is not supported (up to 8)", taps_);
+    }
   }
-  std::vector<Part *> parts() const { return {mixer_norm_.get(), mixer_.get(), ff_norm_.get(), ff_.get()}; }
+  std::vector<Part *> parts() const {
+    std::vector<Part *> p = {mixer_norm_.get(), mixer_.get()};
+    if (ff_) {
+      p.push_back(ff_norm_.get());
+      p.push_back(ff_.get());
+    }
+    return p;
+  }
   Mixer *mixer_part() override { return mixer_.get(); }
+  std::vector<StateNeed> state_need() override {
+    std::vector<StateNeed> needs;
+    if (taps_ > 1) needs.push_back({CONV_STATE, {(int64_t)taps_ - 1, hidden_}, env_.dtype});
+    for (auto &n : mixer_->state_need()) needs.push_back(n);
+    return needs;
+  }
   std::vector<TensorNeed> tensor_needs() const override {
     std::vector<TensorNeed> out;
     for (Part *p : parts())
       for (auto &n : p->tensor_needs()) out.push_back(n);
+    if (taps_ > 0) out.push_back({conv_name_, {hidden_, (int64_t)taps_}, TensorRole::Vector, false});
     return out;
   }
   void load(const Loader &l) override {
     for (Part *p : parts()) p->load(l);
+    if (taps_ > 0) conv_ = l.fetch({conv_name_, {hidden_, (int64_t)taps_}, TensorRole::Vector, false});
   }
   std::vector<std::string> kernel_families() const override {
     std::vector<std::string> out;
     for (Part *p : parts())
       for (auto &f : p->kernel_families()) out.push_back(f);
+    if (taps_ > 0) out.push_back("recurrent");
     return out;
   }
   bool capturable() const override {
@@ -507,6 +615,22 @@ class PreNormBlock : public Block {
       ctx.sink_cols = stream.hidden;
     };
     Act h = mixer_norm_->forward(ctx, stream);
+    StateView mixer_state;
+    if (taps_ > 0) {
+      void *conv_state = nullptr;
+      if (state)
+        for (const auto &t : *state) {
+          if (t.name == CONV_STATE) conv_state = t.data;
+          else mixer_state.push_back(t);
+        }
+      if (taps_ > 1 && !conv_state) LLM_THROW(InvalidArg, "prenorm block: the run has no state for its convolution");
+      flush_chain(ctx);
+      Act mixed = ctx.arena->act(ctx.dtype, h.rows, h.cols);
+      kernels::causal_conv(h, mixed, conv_.buf.as<float>(), conv_state, ctx.tok_seq, ctx.tok_pos, ctx.seq_start, ctx.seq_past,
+                           ctx.seq_slot, ctx.n_seqs, taps_, ctx.decode_only, ctx.stream);
+      h = mixed;
+      state = mixer_state.empty() ? nullptr : &mixer_state;
+    }
     sink(true);
     Act r = mixer_->forward(ctx, h, cache, state);
     sink(false);
@@ -516,6 +640,7 @@ class PreNormBlock : public Block {
       stream.pending = Act();
       return;
     }
+    if (!ff_) return;
     if (ctx.rows_read_after && ctx.n_rows_read_after < stream.rows && !stream.picked) {
       // the last layer of a prompt step: the feed-forward of the wanted rows alone
       flush_chain(ctx);
@@ -539,6 +664,10 @@ class PreNormBlock : public Block {
   std::unique_ptr<Norm> mixer_norm_, ff_norm_;
   std::unique_ptr<Mixer> mixer_;
   std::unique_ptr<FeedForward> ff_;
+  int taps_ = 0;
+  int64_t hidden_ = 0;
+  std::string conv_name_;
+  Weight conv_;
 };
 
 // ---------------------------------------------------------------- parallel block
@@ -673,11 +802,14 @@ PartFactory factory_of() {
 void register_part_raw(const std::string &category, const std::string &kind, PartFactory factory);   // parts/part.cc
 
 void register_feed_forward_parts();   // parts/feed_forward.cc
+void register_recurrent_parts();      // parts/recurrent.cc
 
 void register_builtin_parts() {
   register_part_raw("block", "parallel", factory_of<ParallelBlock>());
   register_feed_forward_parts();
+  register_recurrent_parts();
   register_part_raw("norm", "rmsnorm", factory_of<RMSNorm>());
+  register_part_raw("norm", "layernorm", factory_of<LayerNorm>());
   register_part_raw("position", "rope", factory_of<RotaryEmbedding>());
   register_part_raw("mixer", "attention", factory_of<Attention>());
   register_part_raw("feed_forward", "swiglu", factory_of<SwiGLU>());

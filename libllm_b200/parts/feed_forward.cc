@@ -16,7 +16,8 @@ int activation_code(const std::string &name, const ConfigReader &r) {
   if (name == "gelu") return kernels::GeluErf;          // 0.5 z (1 + erf(z / sqrt 2))
   if (name == "gelu_tanh") return kernels::GeluTanh;    // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
   if (name == "silu") return kernels::Silu;
-  r.fail("activation '" + name + "' is not known (gelu, gelu_tanh, silu)");
+  if (name == "relu2") return kernels::Relu2;           // max(z, 0)^2
+  r.fail("activation '" + name + "' is not known (gelu, gelu_tanh, silu, relu2)");
 }
 
 // ---------------------------------------------------------------- up, activation, down
@@ -64,7 +65,9 @@ class Mlp : public FeedForward {
 // expert(w x); "output": of w expert(x).  Experts are two-matrix feed-forwards whose tensors are
 // named by a pattern with "{}" for the expert's number; they lie stacked on the device,
 // [experts, ff, hidden] and [experts, hidden, ff].  A `shared` feed-forward (any description) runs
-// for every token and is added.  The result is [parts, T, hidden]: a part per choice, then the
+// for every token and is added.  With `expert.gate` (a third pattern) an expert is down(act(gate x) * up x); its
+// gate and up rows lie interleaved in one stacked matrix [experts, 2 ff, hidden] and the weight goes on the
+// output.  The result is [parts, T, hidden]: a part per choice, then the
 // shared one's, which the stream adds in that order.
 class RoutedFeedForward : public FeedForward {
  public:
@@ -87,8 +90,11 @@ class RoutedFeedForward : public FeedForward {
     act_ = activation_code(e.string_or("activation", "gelu"), e);
     up_ = e.string("up");
     down_ = e.string("down");
-    if (up_.find("{}") == std::string::npos || down_.find("{}") == std::string::npos)
-      e.fail("'up' and 'down' are patterns with \"{}\" for the expert's number");
+    gate_ = e.string_or("gate", "");
+    if (up_.find("{}") == std::string::npos || down_.find("{}") == std::string::npos ||
+        (!gate_.empty() && gate_.find("{}") == std::string::npos))
+      e.fail("'up', 'down' and 'gate' are patterns with \"{}\" for the expert's number");
+    if (!gate_.empty() && !weight_on_output_) e.fail("gated experts take their weight on the output");
     if (r.present("shared")) shared_ = build_as<FeedForward>("feed_forward", r.object("shared"), env);
   }
   static std::string numbered(const std::string &pattern, int e) {
@@ -101,6 +107,7 @@ class RoutedFeedForward : public FeedForward {
     for (int e = 0; e < experts_; ++e) {
       needs.push_back({numbered(up_, e), {inter_, hidden_}});
       needs.push_back({numbered(down_, e), {hidden_, inter_}});
+      if (!gate_.empty()) needs.push_back({numbered(gate_, e), {inter_, hidden_}});
     }
     if (shared_)
       for (auto &n : shared_->tensor_needs()) needs.push_back(n);
@@ -110,11 +117,24 @@ class RoutedFeedForward : public FeedForward {
     const auto needs = tensor_needs();
     w_router_ = l.fetch(needs[0]);
     const size_t es = dtype_size(l.engine), one = (size_t)(inter_ * hidden_) * es;
-    w_up_.allocate(one * (size_t)experts_);
+    const bool gated = !gate_.empty();
+    const size_t per = gated ? 3 : 2, row = (size_t)hidden_ * es;
+    w_up_.allocate(one * (size_t)experts_ * (gated ? 2 : 1));
     w_down_.allocate(one * (size_t)experts_);
+    DeviceBuffer staged;
+    if (gated) staged.allocate(one);
     for (int e = 0; e < experts_; ++e) {
-      l.fetch_into(needs[1 + 2 * (size_t)e], l.engine, (char *)w_up_.get() + one * (size_t)e);
-      l.fetch_into(needs[2 + 2 * (size_t)e], l.engine, (char *)w_down_.get() + one * (size_t)e);
+      l.fetch_into(needs[2 + per * (size_t)e], l.engine, (char *)w_down_.get() + one * (size_t)e);
+      if (!gated) {
+        l.fetch_into(needs[1 + per * (size_t)e], l.engine, (char *)w_up_.get() + one * (size_t)e);
+        continue;
+      }
+      // row 2n: the gate's row n; row 2n + 1: the up row n
+      char *dst = (char *)w_up_.get() + 2 * one * (size_t)e;
+      for (int half = 0; half < 2; ++half) {
+        l.fetch_into(needs[(half == 0 ? 3 : 1) + per * (size_t)e], l.engine, staged.get());
+        LLM_CUDA(cudaMemcpy2D(dst + (size_t)half * row, 2 * row, staged.get(), row, row, (size_t)inter_, cudaMemcpyDeviceToDevice));
+      }
     }
     if (shared_) shared_->load(l);
   }
@@ -154,7 +174,7 @@ class RoutedFeedForward : public FeedForward {
       void *mid = ctx.arena->alloc((size_t)n_rows * (size_t)inter_ * 2);
       kernels::moe_sort(chosen, n_rows, experts_, tile, offsets, perm, tiles, ctx.stream);
       kernels::moe_tc(x, w_up_.get(), w_down_.get(), offsets, perm, tiles, weight, experts_, top_, (int)hidden_, (int)inter_, act_,
-                      weight_on_output_, xs, mid, (float *)out.data, ctx.tc_status, ctx.stream);
+                      weight_on_output_, xs, mid, (float *)out.data, ctx.tc_status, ctx.stream, !gate_.empty());
     } else if (aligned && kernels::moe_grouped_supported((int)hidden_, (int)inter_)) {
       const int tile = kernels::moe_tile_rows();
       int *offsets = ctx.arena->alloc_n<int>((size_t)experts_ + 1);
@@ -163,10 +183,10 @@ class RoutedFeedForward : public FeedForward {
       void *mid = ctx.arena->alloc((size_t)n_rows * (size_t)inter_ * 2);
       kernels::moe_sort(chosen, n_rows, experts_, tile, offsets, perm, tiles, ctx.stream);
       kernels::moe_grouped(x, w_up_.get(), w_down_.get(), offsets, perm, tiles, weight, experts_, top_, (int)hidden_, (int)inter_,
-                           act_, weight_on_output_, mid, (float *)out.data, ctx.stream);
+                           act_, weight_on_output_, mid, (float *)out.data, ctx.stream, !gate_.empty());
     } else {
       kernels::moe_rows(x, w_up_.get(), w_down_.get(), chosen, weight, top_, (int)hidden_, (int)inter_, act_, weight_on_output_,
-                        (float *)out.data, ctx.stream);
+                        (float *)out.data, ctx.stream, !gate_.empty());
     }
     if (s_own) {
       if (s.dtype != DType::F32 || s.rows != T || s.cols != hidden_ || s.ld != hidden_)
@@ -183,7 +203,7 @@ class RoutedFeedForward : public FeedForward {
   int64_t hidden_, inter_;
   int experts_, top_, score_, act_;
   bool renormalize_, weight_on_output_;
-  std::string router_, up_, down_;
+  std::string router_, up_, down_, gate_;
   Weight w_router_;
   DeviceBuffer w_up_, w_down_;
   std::unique_ptr<FeedForward> shared_;

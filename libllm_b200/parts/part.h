@@ -46,7 +46,8 @@ struct BuildEnv {
 
 // Keys and values a mixer wants kept per sequence.  kind "full" keeps every position, "window"
 // only the last `window` (older pages are given back), "block" only the positions of the block of
-// `block` positions (counted from 0) that the next token falls into.  Keys and values have widths of their
+// `block` positions (counted from 0) that the next token falls into.  With `sink` a "window" also keeps the
+// first `sink` positions of the sequence for good.  Keys and values have widths of their
 // own; v_dim 0 keeps one vector per position (a latent) in the key storage alone.
 struct CacheNeed {
   std::string kind = "full";
@@ -55,9 +56,10 @@ struct CacheNeed {
   int v_dim = 0;
   int window = 0;                    // 0: none
   int block = 0;                     // 0: none
+  int sink = 0;                      // first positions that a window keeps
   bool operator==(const CacheNeed &o) const {
     return kind == o.kind && n_kv_heads == o.n_kv_heads && k_dim == o.k_dim && v_dim == o.v_dim && window == o.window &&
-           block == o.block;
+           block == o.block && sink == o.sink;
   }
 };
 
@@ -186,6 +188,11 @@ class Loader {
   // Converts the tensor of `need` to `target` and puts it at `dst` on the device.
   virtual void fetch_into(const TensorNeed &need, DType target, void *dst) const = 0;
   virtual bool has(const std::string &name) const = 0;
+  // The shape a tensor is stored with; empty when the loader draws its tensors (they have the shape asked for).
+  virtual std::vector<int64_t> shape_of(const std::string &name) const {
+    (void)name;
+    return {};
+  }
   // The same into a new buffer, in the type the need's role calls for.
   Weight fetch(const TensorNeed &need) const;
   const DType engine;
@@ -259,6 +266,11 @@ class Block : public Part {
  public:
   using Part::Part;
   virtual Mixer *mixer_part() = 0;
+  // Fixed-size state per sequence of one run of the block: the mixer's, and what the block keeps itself.
+  virtual std::vector<StateNeed> state_need() {
+    Mixer *m = mixer_part();
+    return m ? m->state_need() : std::vector<StateNeed>();
+  }
   virtual void forward(StepContext &ctx, ResidualStream &stream, LayerCache *cache, StateView *state) = 0;
 };
 

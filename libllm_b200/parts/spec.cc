@@ -10,6 +10,7 @@ Json ModelSpec::to_json() const {
   j.set("vocab_size", vocab_size);
   j.set("hidden", hidden);
   j.set("embedding", embedding);
+  j.set("position_table", position_table.empty() ? Json() : Json(position_table));
   Json ls = Json::array();
   for (const auto &l : layers) ls.push(l);
   j.set("layers", ls);
@@ -41,6 +42,7 @@ ModelSpec ModelSpec::from_json(const Json &j) {
   s.vocab_size = r.integer("vocab_size");
   s.hidden = r.integer("hidden");
   s.embedding = r.string("embedding");
+  s.position_table = r.string_or("position_table", "");
   const Json &ls = j.get("layers");
   if (!ls.is_array()) r.fail("'layers' must be a list of block descriptions");
   for (const auto &l : ls.items()) {

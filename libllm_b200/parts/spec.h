@@ -10,6 +10,8 @@
 // here are the arguments of those build functions.
 //
 //   norm "rmsnorm":        size, eps, weight (tensor name)
+//   norm "layernorm":      size, eps, weight, bias (tensor names; bias optional)
+//   mixer "general_delta": hidden, n_heads, head_dim, eps, decay_rank, decay_scale, key_eps, tensor names (parts/recurrent.cc)
 //   position "rope":       head_dim, rotary_dim, theta, scaling (null or the llama3 parameters)
 //   mixer "attention":     hidden, n_heads, n_kv_heads, head_dim, v_head_dim (default head_dim),
 //                          position (a position description or null), window (null: all keys),
@@ -18,7 +20,7 @@
 //   mixer "attention" also: v_head_dim, qk_norm {q, k, eps}, block (mask), head_gate (parts/builtin.cc)
 //   feed_forward "mlp":    hidden, intermediate, activation (gelu, gelu_tanh, silu), up, down
 //   feed_forward "moe":    hidden, experts, top, score, renormalize, weight_on, router, expert {..}, shared
-//   block "prenorm":       mixer_norm, mixer, ff_norm, ff (descriptions)
+//   block "prenorm":       mixer_norm, mixer, ff_norm, ff (descriptions; ff and ff_norm may be null), mixer_conv {taps, weight, hidden}
 //   block "parallel":      norm, mixer, ff (a description or null): x + mixer(norm x) + ff(norm x)
 #pragma once
 #include <string>
@@ -45,6 +47,7 @@ struct ModelSpec {
   int64_t vocab_size = 0;
   int64_t hidden = 0;
   std::string embedding;                  // tensor name of the token table
+  std::string position_table;             // [max_positions, hidden]: a learned vector per position, added to the token's row; empty: none
   std::vector<Json> layers;               // block descriptions
   std::vector<ScheduleEntry> schedule;
   Json final_norm;

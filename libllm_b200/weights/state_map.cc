@@ -37,6 +37,13 @@ bool name_matches(const std::string &pattern, const std::string &name) {
   return p == pattern.size();
 }
 
+bool shape_fits(const std::vector<int64_t> &wanted, const std::vector<int64_t> &found) {
+  if (wanted.size() != found.size()) return false;
+  for (size_t i = 0; i < wanted.size(); ++i)
+    if (wanted[i] >= 0 && wanted[i] != found[i]) return false;
+  return true;
+}
+
 std::string shape_text(const std::vector<int64_t> &shape) {
   std::string s = "(";
   for (size_t i = 0; i < shape.size(); ++i) s += (i ? ", " : "") + std::to_string(shape[i]);
@@ -117,7 +124,7 @@ WeightsReport StateMap::check(const std::vector<TensorNeed> &needs, const std::v
       continue;
     }
     const auto &found = tensors_.at(n.name).shape;
-    if (found != n.shape) r.wrong_shape.push_back({n.name, n.shape, found});
+    if (!shape_fits(n.shape, found)) r.wrong_shape.push_back({n.name, n.shape, found});
   }
   for (const auto &n : names_) {
     if (wanted.count(n)) continue;
@@ -186,7 +193,7 @@ int64_t read_int(const uint8_t *p, StoredType t, int64_t i) {
 
 void StateMap::fetch_into(const TensorNeed &need, DType target, void *dst) const {
   const StoredTensor &t = stored(need.name);
-  if (t.shape != need.shape) {
+  if (!shape_fits(need.shape, t.shape)) {
     WeightsReport r;
     r.wrong_shape.push_back({need.name, need.shape, t.shape});
     throw WeightsError(need.name + ": invalid shape: " + shape_text(need.shape) + " expected, but " + shape_text(t.shape) + " found.", r);

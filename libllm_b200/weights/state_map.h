@@ -22,6 +22,9 @@ namespace llm {
 
 enum class TensorRole { Matrix, Vector, Table };
 
+// A size of -1 in `shape` is free: the tensor's own size there is taken (the part that asked reads it from the
+// loader when it loads); where tensors are drawn instead of read, a free size becomes DRAWN_FREE_SIZE.
+constexpr int64_t DRAWN_FREE_SIZE = 16;
 struct TensorNeed {
   std::string name;
   std::vector<int64_t> shape;
@@ -45,6 +48,7 @@ class WeightsError : public Error {
   WeightsReport report;
 };
 
+bool shape_fits(const std::vector<int64_t> &wanted, const std::vector<int64_t> &found);   // -1 fits any size
 bool name_matches(const std::string &pattern, const std::string &name);   // '*' matches any run of characters
 std::string shape_text(const std::vector<int64_t> &shape);
 
