@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(AD_THREADS)
 attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
                         const __nv_bfloat16 *__restrict__ kc, const __nv_bfloat16 *__restrict__ vc,
                         const int *__restrict__ tok_pos, const int *__restrict__ page_table, int pt_stride,
-                        int n_kv, int page_size, int chunk, int window, int block, float scale_log2,
+                        int n_kv, int page_size, int chunk, int window, int block, int sink, float scale_log2,
                         float *__restrict__ ws_o, float *__restrict__ ws_ml, int n_splits,
                         __nv_bfloat16 *__restrict__ out, long long out_stride, const float *__restrict__ gate,
                         long long gate_stride) {
@@ -55,9 +55,11 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int len = tok_pos[b] + 1;
   const int kstart = max(window > 0 ? max(0, len - window) : 0, block > 0 ? (len - 1) / block * block : 0);
+  // the first `sink` positions stay visible beyond the window: keys [0, sink_end) and [kstart, len)
+  const int sink_end = (window > 0 && block == 0) ? min(sink, kstart) : 0;
   const int c0 = split * chunk;
   const int c1 = min(c0 + chunk, len);
-  if (c0 >= len || c1 <= kstart) {
+  if (c0 >= len || (c1 <= kstart && c0 >= sink_end)) {
     grid_dependency_wait();
     return;
   }
@@ -100,8 +102,9 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
       const int key = base + u * GROUPS + grp;
       // A key that exists and lies inside the window (its weight is zero): pages before
       // the window may have been given back, and their table entries are not page numbers.
+      // (Between the kept first positions and the window likewise: a kept key of this chunk, or the window's first.)
       int kk = key < c1 ? key : c1 - 1;
-      kk = kk < kstart ? kstart : kk;
+      if (kk < kstart && kk >= sink_end) kk = c0 < sink_end ? c0 : (kstart < c1 ? kstart : c1 - 1);
       const int page = s_pages[(kk - c0) / page_size];
       const size_t off = (((size_t)page * n_kv + kvh) * page_size + (kk % page_size)) * D + sub * 8;
       kr[u] = *reinterpret_cast<const uint4 *>(kc + off);
@@ -113,7 +116,7 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
 #pragma unroll
     for (int u = 0; u < AD_KB; ++u) {
       const int key = base + u * GROUPS + grp;
-      ok[u] = key < c1 && key >= kstart;
+      ok[u] = key < c1 && (key >= kstart || key < sink_end);
     }
     float s[AD_KB][G];
 #pragma unroll
@@ -232,7 +235,7 @@ attention_decode_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride,
 // Joins the splits of one (sequence, head): out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
 __global__ void attention_decode_combine_kernel(const float *__restrict__ ws_o, const float *__restrict__ ws_ml,
                                                 const int *__restrict__ tok_pos, int n_heads, int D, int chunk,
-                                                int window, int block, int n_splits, __nv_bfloat16 *__restrict__ out,
+                                                int window, int block, int sink, int n_splits, __nv_bfloat16 *__restrict__ out,
                                                 long long out_stride, const float *__restrict__ gate,
                                                 long long gate_stride) {
   grid_dependents_launch();
@@ -243,16 +246,22 @@ __global__ void attention_decode_combine_kernel(const float *__restrict__ ws_o, 
   // Splits beyond n_splits do not exist (the caller's n_splits * chunk should cover the longest
   // sequence; keys beyond it were not attended to): never read another head's scratch.
   const int first = min(kstart / chunk, n_splits - 1), last = min((len - 1) / chunk, n_splits - 1);
+  // splits before `first` hold kept first positions as far as they begin before sink_end; the others wrote nothing
+  const int sink_end = (window > 0 && block == 0) ? min(sink, kstart) : 0;
+  auto live = [&](int s) { return s >= first || s * chunk < sink_end; };
   const size_t slot0 = ((size_t)b * n_heads + head) * n_splits;
   float M = -INFINITY;
-  for (int s = first; s <= last; ++s) M = fmaxf(M, ws_ml[(slot0 + s) * 2]);
+  for (int s = 0; s <= last; ++s)
+    if (live(s)) M = fmaxf(M, ws_ml[(slot0 + s) * 2]);
   float L = 0.f;
-  for (int s = first; s <= last; ++s) L += ws_ml[(slot0 + s) * 2 + 1] * exp2f(ws_ml[(slot0 + s) * 2] - M);
+  for (int s = 0; s <= last; ++s)
+    if (live(s)) L += ws_ml[(slot0 + s) * 2 + 1] * exp2f(ws_ml[(slot0 + s) * 2] - M);
   // a gate per (sequence, head): the result is multiplied by its sigmoid
   const float gf = gate ? 1.f / (1.f + expf(-gate[(size_t)b * gate_stride + head])) : 1.f;
   for (int c = threadIdx.x; c < D; c += blockDim.x) {
     float O = 0.f;
-    for (int s = first; s <= last; ++s) O += ws_o[(slot0 + s) * D + c] * exp2f(ws_ml[(slot0 + s) * 2] - M);
+    for (int s = 0; s <= last; ++s)
+      if (live(s)) O += ws_o[(slot0 + s) * D + c] * exp2f(ws_ml[(slot0 + s) * 2] - M);
     out[(size_t)b * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(O / L * gf);
   }
 }
@@ -260,20 +269,20 @@ __global__ void attention_decode_combine_kernel(const float *__restrict__ ws_o, 
 template <int D, int G>
 static int launch_decode(const void *q, long long q_stride, const void *kc, const void *vc, const int *tok_pos,
                          const int *page_table, int pt_stride, int n_seqs, int n_kv, int page_size, int chunk,
-                         int n_splits, int window, int block, float scale, float *ws_o, float *ws_ml, void *out,
+                         int n_splits, int window, int block, int sink, float scale, float *ws_o, float *ws_ml, void *out,
                          long long out_stride, const float *gate, long long gate_stride, cudaStream_t stream) {
   dim3 grid(n_splits, n_kv, n_seqs);
   const size_t smem = (size_t)((chunk + page_size - 1) / page_size) * sizeof(int);
   LLM_REQUIRE(smem <= 16 * 1024, "attention_decode: a chunk of %d keys spans too many pages", chunk);
   llm_launch(attention_decode_kernel<D, G>, grid, dim3(AD_THREADS), smem, stream,
       (const __nv_bfloat16 *)q, q_stride, (const __nv_bfloat16 *)kc, (const __nv_bfloat16 *)vc, tok_pos, page_table,
-      pt_stride, n_kv, page_size, chunk, window, block, scale * 1.4426950408889634f, ws_o, ws_ml, n_splits,
+      pt_stride, n_kv, page_size, chunk, window, block, sink, scale * 1.4426950408889634f, ws_o, ws_ml, n_splits,
       (__nv_bfloat16 *)out, out_stride, gate, gate_stride);
   LLM_CHECK_LAUNCH("attention_decode");
   if (n_splits > 1) {
     dim3 cgrid(n_kv * G, n_seqs);
     llm_launch(attention_decode_combine_kernel, cgrid, dim3(D < 64 ? 32 : 64), 0, stream, (const float *)ws_o,
-               (const float *)ws_ml, tok_pos, n_kv * G, D, chunk, window, block, n_splits, (__nv_bfloat16 *)out, out_stride,
+               (const float *)ws_ml, tok_pos, n_kv * G, D, chunk, window, block, sink, n_splits, (__nv_bfloat16 *)out, out_stride,
                gate, gate_stride);
     LLM_CHECK_LAUNCH("attention_decode_combine");
   }
@@ -291,13 +300,14 @@ LLM_EXPORT int llm_attention_decode_supports(int d, int group) {
 // position of sequence b's query (it sees keys 0..tok_pos[b]).  ws_o needs
 // B*heads*n_splits*d floats and ws_ml B*heads*n_splits*2 when n_splits > 1.
 // `gate` (32-bit, one value per sequence and head, row stride gate_stride; null: none): a head's result is
-// multiplied by sigmoid(gate).
-LLM_EXPORT int llm_attention_decode_gated(const void *q, long long q_stride, void *out, long long out_stride,
-                                          const void *kc, const void *vc, const int *tok_pos, const int *page_table,
-                                          int pt_stride, int n_seqs, int n_heads, int n_kv, int d, int page_size,
-                                          int chunk, int n_splits, int window, int block, float scale, float *ws_o,
-                                          float *ws_ml, const float *gate, long long gate_stride, cudaStream_t stream) {
+// multiplied by sigmoid(gate).  `sink` > 0 with a window: the first `sink` positions stay visible beyond the window.
+LLM_EXPORT int llm_attention_decode_sink(const void *q, long long q_stride, void *out, long long out_stride,
+                                         const void *kc, const void *vc, const int *tok_pos, const int *page_table,
+                                         int pt_stride, int n_seqs, int n_heads, int n_kv, int d, int page_size,
+                                         int chunk, int n_splits, int window, int block, int sink, float scale, float *ws_o,
+                                         float *ws_ml, const float *gate, long long gate_stride, cudaStream_t stream) {
   if (n_seqs == 0) return LLM_OK;
+  LLM_REQUIRE(sink >= 0 && (sink == 0 || (window > 0 && block == 0)), "attention_decode: kept first positions go with a window");
   LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_kv > 0 && n_kv <= 65535 && n_heads % n_kv == 0, "attention_decode: bad sizes");
   const int group = n_heads / n_kv;
   LLM_REQUIRE(llm_attention_decode_supports(d, group), "attention_decode: head size %d with %d query heads per kv head is not built", d, group);
@@ -307,13 +317,22 @@ LLM_EXPORT int llm_attention_decode_gated(const void *q, long long q_stride, voi
 #define AD_CASE(DD, GG)                                                                                         \
   if (d == DD && group == GG)                                                                                   \
     return launch_decode<DD, GG>(q, q_stride, kc, vc, tok_pos, page_table, pt_stride, n_seqs, n_kv, page_size, \
-                                 chunk, n_splits, window, block, scale, ws_o, ws_ml, out, out_stride, gate, gate_stride, \
+                                 chunk, n_splits, window, block, sink, scale, ws_o, ws_ml, out, out_stride, gate, gate_stride, \
                                  stream);
 #define AD_CASES(DD) AD_CASE(DD, 1) AD_CASE(DD, 2) AD_CASE(DD, 3) AD_CASE(DD, 4) AD_CASE(DD, 8)
   AD_CASES(16) AD_CASES(32) AD_CASES(64) AD_CASES(128)
 #undef AD_CASES
 #undef AD_CASE
   LLM_FAIL("attention_decode: no kernel for head size %d, group %d", d, group);
+}
+
+LLM_EXPORT int llm_attention_decode_gated(const void *q, long long q_stride, void *out, long long out_stride,
+                                          const void *kc, const void *vc, const int *tok_pos, const int *page_table,
+                                          int pt_stride, int n_seqs, int n_heads, int n_kv, int d, int page_size,
+                                          int chunk, int n_splits, int window, int block, float scale, float *ws_o,
+                                          float *ws_ml, const float *gate, long long gate_stride, cudaStream_t stream) {
+  return llm_attention_decode_sink(q, q_stride, out, out_stride, kc, vc, tok_pos, page_table, pt_stride, n_seqs, n_heads, n_kv, d,
+                                   page_size, chunk, n_splits, window, block, 0, scale, ws_o, ws_ml, gate, gate_stride, stream);
 }
 
 LLM_EXPORT int llm_attention_decode(const void *q, long long q_stride, void *out, long long out_stride,

@@ -37,7 +37,7 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
                          long long out_stride, const __nv_bfloat16 *__restrict__ kc,
                          const __nv_bfloat16 *__restrict__ vc, const int *__restrict__ seq_start,
                          const int *__restrict__ seq_past, const int *__restrict__ page_table, int pt_stride,
-                         int n_heads, int n_kv, int window, int block, float scale_log2) {
+                         int n_heads, int n_kv, int window, int block, int sink, float scale_log2) {
   constexpr int LD = D + 8;                                  // padded row, in elements
   constexpr int CHUNKS = D / 8;                              // 16-byte pieces of a row
   constexpr int KS = D / 16;                                 // k-steps of Q K^T
@@ -68,6 +68,12 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
   // keys before this one are hidden from the CTA's last row by the block mask (0: no such mask)
   const int block_edge = block > 0 ? (past + r0 + rows - 1) / block * block : 0;
   const int *pt = page_table + (size_t)b * pt_stride;
+  // A window that keeps the first `sink` positions: their tiles, as far as they lie before the window's
+  // first tile, are walked first (the pages between them and the window may be gone).  Step `it` of the
+  // walk is tile it (it < n_sink) or first_tile + it - n_sink.
+  const int n_sink = (sink > 0 && window > 0 && block == 0) ? min(first_tile, (sink + AP_BN - 1) / AP_BN) : 0;
+  const int n_iter = n_sink + last_tile - first_tile + 1;
+  auto tile_of = [&](int it) { return it < n_sink ? it : first_tile + it - n_sink; };
 
   auto load_kv = [&](int kt, int stage) {
     const int page = pt[kt];
@@ -86,7 +92,7 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
     const bool ok = r < rows;
     cp_async16(sQ + r * LD + ch * 8, q + (size_t)(q0 + r0 + (ok ? r : 0)) * q_stride + (size_t)h * D + ch * 8, ok);
   }
-  load_kv(first_tile, 0);
+  load_kv(tile_of(0), 0);
   cp_async_commit();
 
   unsigned qf[KS][4];
@@ -99,13 +105,14 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
   // absolute positions of this thread's two rows
   const int pos0 = past + r0 + warp * 16 + g, pos1 = pos0 + 8;
 
-  for (int kt = first_tile; kt <= last_tile; ++kt) {
-    const int stage = (kt - first_tile) & 1;
-    if (kt + 1 <= last_tile) load_kv(kt + 1, stage ^ 1);
+  for (int it = 0; it < n_iter; ++it) {
+    const int kt = tile_of(it);
+    const int stage = it & 1;
+    if (it + 1 < n_iter) load_kv(tile_of(it + 1), stage ^ 1);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
-    if (kt == first_tile) {
+    if (it == 0) {
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks)
         ldmatrix_x4(qf[ks], sQ + (warp * 16 + (lane & 15)) * LD + ks * 16 + (lane >> 4) * 8);
@@ -130,7 +137,7 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
 
     // mask: key j is seen by the row at position p when j <= p and (no window or j > p - window)
     const int k0 = kt * AP_BN;
-    const bool edge = (k0 + AP_BN - 1 > past + r0) || (window > 0 && k0 <= past + r0 + AP_BM - 1 - window) || k0 < block_edge;
+    const bool edge = (k0 + AP_BN - 1 > past + r0) || (window > 0 && k0 <= past + r0 + AP_BM - 1 - window) || k0 < block_edge;   // kept first positions lie in such tiles
     if (edge) {
 #pragma unroll
       for (int n = 0; n < NT; ++n)
@@ -138,7 +145,7 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
         for (int j = 0; j < 4; ++j) {
           const int key = k0 + n * 8 + 2 * t + (j & 1);
           const int p = (j & 2) ? pos1 : pos0;
-          const bool seen = key <= p && (window <= 0 || key > p - window) && (block <= 0 || key >= p / block * block);
+          const bool seen = key <= p && (window <= 0 || key > p - window || key < sink) && (block <= 0 || key >= p / block * block);
           if (!seen) s[n][j] = -INFINITY;
         }
     }
@@ -221,7 +228,7 @@ attention_prefill_kernel(const __nv_bfloat16 *__restrict__ q, long long q_stride
 template <int D>
 static int launch_prefill(const void *q, long long q_stride, void *out, long long out_stride, const void *kc,
                           const void *vc, const int *seq_start, const int *seq_past, const int *page_table,
-                          int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int window, int block, float scale,
+                          int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int window, int block, int sink, float scale,
                           cudaStream_t stream) {
   constexpr int LD = D + 8;
   const size_t smem = (size_t)(AP_BM + 4 * AP_BN) * LD * sizeof(__nv_bfloat16);
@@ -230,7 +237,7 @@ static int launch_prefill(const void *q, long long q_stride, void *out, long lon
   dim3 grid((max_q_len + AP_BM - 1) / AP_BM, n_heads, n_seqs);
   llm_launch(kern, grid, dim3(AP_WARPS * 32), smem, stream, (const __nv_bfloat16 *)q, q_stride, (__nv_bfloat16 *)out,
              out_stride, (const __nv_bfloat16 *)kc, (const __nv_bfloat16 *)vc, seq_start, seq_past, page_table,
-             pt_stride, n_heads, n_kv, window, block, scale * 1.4426950408889634f);
+             pt_stride, n_heads, n_kv, window, block, sink, scale * 1.4426950408889634f);
   LLM_CHECK_LAUNCH("attention_prefill");
   return LLM_OK;
 }
@@ -243,11 +250,14 @@ LLM_EXPORT int llm_attention_prefill_supports(int d, int page_size) {
 // q [tokens, >= heads*d] bfloat16 (rotated), out [tokens, heads*d], caches
 // [pages, kv_heads, 64, d]; sequence b owns rows seq_start[b]..seq_start[b+1]-1, which
 // stand at positions seq_past[b].. of the sequence; max_q_len bounds the rows of a sequence.
+// `sink` > 0 with a window: the first `sink` positions of a sequence stay visible to all its later queries.
 LLM_EXPORT int llm_attention_prefill(const void *q, long long q_stride, void *out, long long out_stride,
                                      const void *kc, const void *vc, const int *seq_start, const int *seq_past,
                                      const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads,
-                                     int n_kv, int d, int page_size, int window, int block, float scale, cudaStream_t stream) {
+                                     int n_kv, int d, int page_size, int window, int block, int sink, float scale,
+                                     cudaStream_t stream) {
   if (n_seqs == 0 || max_q_len == 0) return LLM_OK;
+  LLM_REQUIRE(sink >= 0 && (sink == 0 || (window > 0 && block == 0)), "attention_prefill: kept first positions go with a window");
   LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_heads > 0 && n_heads <= 65535 && n_kv > 0 && n_heads % n_kv == 0,
               "attention_prefill: bad sizes (%d sequences, %d heads, %d kv heads)", n_seqs, n_heads, n_kv);
   LLM_REQUIRE(llm_attention_prefill_supports(d, page_size),
@@ -260,7 +270,7 @@ LLM_EXPORT int llm_attention_prefill(const void *q, long long q_stride, void *ou
 #define AP_CASE(DD)                                                                                                  \
   if (d == DD)                                                                                                       \
     return launch_prefill<DD>(q, q_stride, out, out_stride, kc, vc, seq_start, seq_past, page_table, pt_stride,      \
-                              n_seqs, max_q_len, n_heads, n_kv, window, block, scale, stream);
+                              n_seqs, max_q_len, n_heads, n_kv, window, block, sink, scale, stream);
   AP_CASE(16) AP_CASE(32) AP_CASE(48) AP_CASE(64) AP_CASE(80) AP_CASE(96) AP_CASE(112) AP_CASE(128)
 #undef AP_CASE
   LLM_FAIL("attention_prefill: no kernel for head size %d", d);

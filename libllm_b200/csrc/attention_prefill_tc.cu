@@ -86,7 +86,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16 *__restrict__ out,
                             long long out_stride, const int *__restrict__ seq_start, const int *__restrict__ seq_past,
                             const int *__restrict__ page_table, int pt_stride, int n_heads, int n_kv, int window, int block,
-                            float scale_log2, int *status) {
+                            int sink, float scale_log2, int *status) {
   using S = FtShape<D>;
   constexpr int STAGES = S::STAGES;
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -155,7 +155,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   // the first key the CTA's first row sees; keys before block_edge are hidden from its last row by the block mask
   const int first_tile = max(window > 0 ? max(0, past + r0 - window + 1) : 0, block > 0 ? (past + r0) / block * block : 0) / FT_BN;
   const int block_edge = block > 0 && active ? (past + r0 + rows - 1) / block * block : 0;
-  const int n_tiles = last_tile - first_tile + 1;             // <= 0: nothing to do
+  // A window that keeps the first `sink` positions: their tiles, as far as they lie before the window's first tile,
+  // are walked first (the pages between them and the window may be gone); step j of the walk is tile_of(j).
+  const int n_sink = (active && sink > 0 && window > 0 && block == 0) ? min(first_tile, (sink + FT_BN - 1) / FT_BN) : 0;
+  const int n_tiles = last_tile - first_tile + 1 + n_sink;    // <= 0: nothing to do
+  auto tile_of = [&](int j) { return j < n_sink ? j : first_tile + j - n_sink; };
   const int *pt = page_table + (size_t)b * pt_stride;
 
   // The loader's and the issuers' loops run in all lanes of their warps (waits, addresses and
@@ -181,7 +185,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int j = 0; j < n_tiles && ok; ++j) {
         ok = __all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, status, 11));
         if (!ok) break;
-        const int row = (pt[first_tile + j] * n_kv + kvh) * FT_BN;
+        const int row = (pt[tile_of(j)] * n_kv + kvh) * FT_BN;
         const unsigned dk = smem_u32(sKV + (size_t)stage * 2 * S::KV_BYTES), dv = dk + S::KV_BYTES;
         if (leader) {
           mbar_expect_tx(bar_full + 8 * stage, 2 * S::KV_BYTES);
@@ -277,7 +281,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int j = 0; j < n_tiles; ++j) {
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * (j & 1), (j >> 1) & 1, abort_flag, status, 18));
       const unsigned s_addr = tmem_s + (j & 1) * FT_BN + lane_addr;
-      const int k0 = (first_tile + j) * FT_BN + half * 32;    // this thread's first key
+      const int k0 = tile_of(j) * FT_BN + half * 32;          // this thread's first key
       float own[2][16];
       float *xrow = xch + (j & 1) * 2 * FT_BM + row;
       if (ok) {
@@ -294,7 +298,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const int key = k0 + c * 16 + i;
-              if (!(key <= pos && key >= vis_lo)) own[c][i] = -INFINITY;
+              if (!(key <= pos && (key >= vis_lo || key < sink))) own[c][i] = -INFINITY;
             }
         }
         float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of sixteen
@@ -822,8 +826,9 @@ template <int D>
 int launch_prefill_tc(const void *q, long long q_stride, long long n_tokens, void *out, long long out_stride,
                       const void *kc, const void *vc, long long n_pages, const int *seq_start, const int *seq_past,
                       const int *page_table, int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int window,
-                      int block, float scale, int form, int *status, cudaStream_t stream) {
+                      int block, int sink, float scale, int form, int *status, cudaStream_t stream) {
   using S = FtShape<D>;
+  if (sink > 0) form = 1;                 // kept first positions: the form of 128 rows walks their tiles
   CUtensorMap map_q, map_k, map_v;
   int rc = get_map(q, n_tokens, (long long)n_heads * D, q_stride, 64, &map_q);
   if (rc != LLM_OK) return rc;
@@ -850,7 +855,7 @@ int launch_prefill_tc(const void *q, long long q_stride, long long n_tokens, voi
   LLM_CHECK_CUDA(llm_allow_smem(kern, S::SMEM), "attention_prefill_tc attribute");
   dim3 grid(n_heads, n_seqs, (max_q_len + FT_BM - 1) / FT_BM);
   LLM_CHECK_CUDA(llm_launch(kern, grid, dim3(FT_THREADS), S::SMEM, stream, map_q, map_k, map_v, (__nv_bfloat16 *)out,
-                            out_stride, seq_start, seq_past, page_table, pt_stride, n_heads, n_kv, window, block,
+                            out_stride, seq_start, seq_past, page_table, pt_stride, n_heads, n_kv, window, block, sink,
                             scale * 1.4426950408889634f, status),
                  "attention_prefill_tc launch");
   return LLM_OK;
@@ -868,13 +873,15 @@ LLM_EXPORT int llm_attention_prefill_tc_supports(int d, int page_size) {
 // positions seq_past[b].. of the sequence; max_q_len bounds the rows of a sequence.  `status` (device
 // int, may be null) receives a non-zero code if a wait inside the kernel ran out of time.  `form`: 0 the
 // library chooses (the wide form when a sequence brings more than 128 rows), 1 CTAs of 128 rows, 2 of 256.
+// `sink` > 0 with a window: the first `sink` positions of a sequence stay visible to all its later queries (form 1).
 LLM_EXPORT int llm_attention_prefill_tc(const void *q, long long q_stride, long long n_tokens, void *out,
                                         long long out_stride, const void *kc, const void *vc, long long n_pages,
                                         const int *seq_start, const int *seq_past, const int *page_table,
                                         int pt_stride, int n_seqs, int max_q_len, int n_heads, int n_kv, int d,
-                                        int page_size, int window, int block, float scale, int form, int *status,
+                                        int page_size, int window, int block, int sink, float scale, int form, int *status,
                                         cudaStream_t stream) {
   if (n_seqs == 0 || max_q_len == 0) return LLM_OK;
+  LLM_REQUIRE(sink >= 0 && (sink == 0 || (window > 0 && block == 0)), "attention_prefill_tc: kept first positions go with a window");
   LLM_REQUIRE(form >= 0 && form <= 2, "attention_prefill_tc: form %d is not one of 0, 1, 2", form);
   LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && n_heads > 0 && n_heads <= 65535 && n_kv > 0 && n_heads % n_kv == 0,
               "attention_prefill_tc: bad sizes (%d sequences, %d heads, %d kv heads)", n_seqs, n_heads, n_kv);
@@ -888,7 +895,7 @@ LLM_EXPORT int llm_attention_prefill_tc(const void *q, long long q_stride, long 
   LLM_REQUIRE(n_pages * n_kv * FT_BN < (1ll << 31), "attention_prefill_tc: the cache has too many rows for one tensor map");
   if (d == 64)
     return launch_prefill_tc<64>(q, q_stride, n_tokens, out, out_stride, kc, vc, n_pages, seq_start, seq_past, page_table,
-                                 pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, block, scale, form, status, stream);
+                                 pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, block, sink, scale, form, status, stream);
   return launch_prefill_tc<128>(q, q_stride, n_tokens, out, out_stride, kc, vc, n_pages, seq_start, seq_past, page_table,
-                                pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, block, scale, form, status, stream);
+                                pt_stride, n_seqs, max_q_len, n_heads, n_kv, window, block, sink, scale, form, status, stream);
 }

@@ -388,7 +388,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, v
                      tok_pos: torch.Tensor, page_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
                      page_size: int, chunk: int, n_splits: int, window: Optional[int], scale: float,
                      ws_o: Optional[torch.Tensor], ws_ml: Optional[torch.Tensor], block: Optional[int] = None,
-                     gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     gate: Optional[torch.Tensor] = None, sink: int = 0) -> torch.Tensor:
     """One query token per sequence over the paged cache, keys split into ``n_splits``
     runs of ``chunk``; ``ws_o``/``ws_ml`` are the scratch the splits are joined through."""
     _on_gpu(q, out, kcache, vcache, tok_pos, page_table, ws_o, ws_ml)
@@ -398,12 +398,12 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, v
     if n_splits > 1:
         assert ws_o.dtype == torch.float32 and ws_o.numel() >= B * n_heads * n_splits * head_dim
         assert ws_ml.dtype == torch.float32 and ws_ml.numel() >= B * n_heads * n_splits * 2
-    _call("attention_decode", "llm_attention_decode_gated",
+    _call("attention_decode", "llm_attention_decode_sink",
           [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p],
+           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p],
           _ptr(q), q.stride(0) if B > 1 else q.shape[1], _ptr(out), out.stride(0) if B > 1 else out.shape[1],
           _ptr(kcache), _ptr(vcache), _ptr(tok_pos), _ptr(page_table), page_table.stride(0), B, n_heads, n_kv,
-          head_dim, page_size, chunk, n_splits, int(window or 0), int(block or 0), float(scale), _ptr(ws_o), _ptr(ws_ml), _ptr(gate),
+          head_dim, page_size, chunk, n_splits, int(window or 0), int(block or 0), int(sink or 0), float(scale), _ptr(ws_o), _ptr(ws_ml), _ptr(gate),
           gate.stride(0) if gate is not None else 0, _stream())
     return out
 
@@ -419,7 +419,7 @@ def attention_prefill_supported(head_dim: int, page_size: int) -> bool:
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                       seq_start: torch.Tensor, seq_past: torch.Tensor, page_table: torch.Tensor, n_seqs: int,
                       max_q_len: int, n_heads: int, n_kv: int, head_dim: int, page_size: int,
-                      window: Optional[int], scale: float, block: Optional[int] = None) -> torch.Tensor:
+                      window: Optional[int], scale: float, block: Optional[int] = None, sink: int = 0) -> torch.Tensor:
     """Causal attention of every sequence's new tokens (rows seq_start[b]..seq_start[b+1]-1 of
     ``q``, standing behind seq_past[b] cached tokens) over the paged cache, which already
     holds the new tokens' keys and values."""
@@ -432,10 +432,10 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, 
     assert tuple(kcache.shape[1:]) == (n_kv, page_size, head_dim)
     _call("attention_prefill", "llm_attention_prefill",
           [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
           _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), _ptr(seq_start),
           _ptr(seq_past), _ptr(page_table), page_table.stride(0), n_seqs, max_q_len, n_heads, n_kv, head_dim,
-          page_size, int(window or 0), int(block or 0), float(scale), _stream())
+          page_size, int(window or 0), int(block or 0), int(sink or 0), float(scale), _stream())
     return out
 
 
@@ -607,7 +607,8 @@ def attention_prefill_tc_supported(head_dim: int, page_size: int) -> bool:
 def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                          seq_start: torch.Tensor, seq_past: torch.Tensor, page_table: torch.Tensor, n_seqs: int,
                          max_q_len: int, n_heads: int, n_kv: int, head_dim: int, page_size: int,
-                         window: Optional[int], scale: float, form: int = 0, block: Optional[int] = None) -> torch.Tensor:
+                         window: Optional[int], scale: float, form: int = 0, block: Optional[int] = None,
+                         sink: int = 0) -> torch.Tensor:
     """The same attention as ``attention_prefill`` with both products on tcgen05 (head sizes 64, 128).
     ``form``: 1 for CTAs of 128 query rows and tiles of 64 keys, 2 for CTAs of 256 rows and tiles of
     128 keys, 0 for the library's choice (the second when a sequence brings more than 128 rows)."""
@@ -618,8 +619,89 @@ def attention_prefill_tc(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tenso
     assert kcache.is_contiguous() and vcache.is_contiguous() and tuple(kcache.shape[1:]) == (n_kv, page_size, head_dim)
     _call("attention_prefill_tc", "llm_attention_prefill_tc",
           [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p,
-           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
           _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(kcache), _ptr(vcache), kcache.shape[0],
           _ptr(seq_start), _ptr(seq_past), _ptr(page_table), page_table.stride(0), n_seqs, max_q_len, n_heads, n_kv,
-          head_dim, page_size, int(window or 0), int(block or 0), float(scale), int(form), _ptr(tc_status(q.device)), _stream())
+          head_dim, page_size, int(window or 0), int(block or 0), int(sink or 0), float(scale), int(form), _ptr(tc_status(q.device)), _stream())
+    return out
+
+
+# ---------------------------------------------------------------- layer norm, kept first positions, carried state
+def add_layernorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, bias: Optional[torch.Tensor],
+                  eps: float, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """resid += sum of delta's parts (32-bit, written back unless ``rows`` selects a subset), then
+    out = (v - mean) / sqrt(var + eps) * weight + bias."""
+    _on_gpu(resid, delta, weight, bias, out, rows)
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and resid.dim() == 2 and out.is_contiguous()
+    T, H = resid.shape
+    n_parts, stride, ddt = 0, 0, F32
+    if delta is not None:
+        assert delta.is_contiguous() and delta.shape[-2:] == resid.shape
+        n_parts, stride, ddt = (1 if delta.dim() == 2 else delta.shape[0]), T * H, dtype_code(delta.dtype)
+    n_rows = T if rows is None else rows.numel()
+    _call("elementwise", "llm_add_layernorm",
+          [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+          _ptr(resid), _ptr(delta), ddt, n_parts, stride, _ptr(weight), _ptr(bias), float(eps), _ptr(out), dtype_code(out.dtype),
+          _ptr(rows), n_rows, H, _stream())
+
+
+def kv_place(qkv: torch.Tensor, q_out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, v_head_dim: int,
+             bias: Optional[torch.Tensor], v_eps: float, tok_seq: torch.Tensor, tok_pos: torch.Tensor, page_table: torch.Tensor,
+             kcache: torch.Tensor, vcache: torch.Tensor, page_size: int, write_cache: bool = True) -> None:
+    """Rows [q | k | v | ...] without a rotation: ``bias`` (one value per stacked row) is added, every value head is
+    divided by its root mean square when ``v_eps`` >= 0; q to ``q_out``, k and v to the paged cache."""
+    _on_gpu(qkv, q_out, bias, tok_seq, tok_pos, page_table, kcache, vcache)
+    assert qkv.stride(1) == 1 and q_out.stride(1) == 1
+    _call("rope", "llm_kv_place",
+          [c_int, c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float,
+           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+          dtype_code(qkv.dtype), dtype_code(q_out.dtype), _ptr(qkv), qkv.stride(0), _ptr(q_out), q_out.stride(0), qkv.shape[0],
+          n_heads, n_kv, head_dim, v_head_dim, _ptr(bias), float(v_eps), _ptr(tok_seq), _ptr(tok_pos), _ptr(page_table),
+          page_table.stride(0), _ptr(kcache), _ptr(vcache), page_size, 1 if write_cache else 0, _stream())
+
+
+def causal_conv(h: torch.Tensor, out: torch.Tensor, weight: torch.Tensor, state: Optional[torch.Tensor], tok_seq: torch.Tensor,
+                tok_pos: torch.Tensor, seq_start: torch.Tensor, seq_past: torch.Tensor, seq_slot: torch.Tensor,
+                single_tokens: bool = False) -> None:
+    """out = h + conv(h) over time per channel; weight [width, taps] 32-bit; state [slots, taps - 1, width] in h's type
+    holds each sequence's last taps - 1 inputs and is moved on."""
+    _on_gpu(h, out, weight, state, tok_seq, tok_pos, seq_start, seq_past, seq_slot)
+    assert h.stride(1) == 1 and out.stride(1) == 1 and weight.dtype == torch.float32 and weight.is_contiguous()
+    _call("recurrent", "llm_causal_conv",
+          [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+           c_int, c_int, c_int, c_int, c_int, c_void_p],
+          dtype_code(h.dtype), _ptr(h), h.stride(0), _ptr(out), out.stride(0), _ptr(weight), _ptr(state), _ptr(tok_seq), _ptr(tok_pos),
+          _ptr(seq_start), _ptr(seq_past), _ptr(seq_slot), h.shape[0], seq_past.numel(), h.shape[1], weight.shape[1],
+          1 if single_tokens else 0, _stream())
+
+
+def delta_rule(proj: torch.Tensor, offsets, rank: int, w2: torch.Tensor, w0: torch.Tensor, a_bias: torch.Tensor,
+               decay_scale: float, key_eps: float, state: torch.Tensor, seq_start: torch.Tensor, seq_slot: torch.Tensor,
+               n_heads: int, d: int) -> torch.Tensor:
+    """The generalized delta rule over 32-bit rows ``proj`` ([T, >= ...]; ``offsets`` of r, k, v, the removal logits and
+    the decay's low-rank input); state [slots, heads, d, d] (a column's rows together) is moved on.  Returns o [T, heads * d]."""
+    _on_gpu(proj, w2, w0, a_bias, state, seq_start, seq_slot)
+    T = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
+    prep = torch.empty(T, n_heads, 3, d, dtype=torch.float32, device=proj.device)
+    out = torch.empty(T, n_heads * d, dtype=torch.float32, device=proj.device)
+    off_r, off_k, off_v, off_a, off_x1 = offsets
+    _call("recurrent", "llm_delta_rule",
+          [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p,
+           c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+          _ptr(proj), proj.stride(0), off_r, off_k, off_v, off_a, off_x1, rank, _ptr(w2), _ptr(w0), _ptr(a_bias), float(decay_scale),
+          float(key_eps), _ptr(prep), _ptr(state), _ptr(out), out.stride(0), _ptr(seq_start), _ptr(seq_slot), T,
+          seq_slot.numel(), n_heads, d, _stream())
+    return out
+
+
+def head_norm_gate(x: torch.Tensor, weight: Optional[torch.Tensor], gate: Optional[torch.Tensor], eps: float, n_heads: int,
+                   dv: int, out: torch.Tensor) -> torch.Tensor:
+    """out[t, h, :] = x / rms(x over the head) (eps < 0: no norm) * weight * sigmoid(gate)."""
+    _on_gpu(x, weight, gate, out)
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and out.stride(1) == 1
+    _call("recurrent", "llm_head_norm_gate",
+          [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_float, c_int, c_int, c_int, c_void_p, c_int, c_longlong, c_void_p],
+          _ptr(x), x.stride(0), _ptr(weight), _ptr(gate), gate.stride(0) if gate is not None else 0, float(eps), x.shape[0], n_heads,
+          dv, _ptr(out), dtype_code(out.dtype), out.stride(0), _stream())
     return out

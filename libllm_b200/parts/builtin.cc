@@ -336,7 +336,6 @@ class Attention : public Mixer {
     if (!plain_) return fams;
     if (!gate_name_.empty()) fams.push_back("elementwise");
     const bool tiled = env_.page_size == 64 && d_ % 16 == 0 && d_ >= 16 && d_ <= 128;
-    if (sink_ > 0) return fams;          // kept first positions: the general kernel
     if (f.prefill_attention_tc && env_.page_size == 64 && (d_ == 64 || d_ == 128)) fams.push_back("attention_prefill_tc");
     else if (f.prefill_attention && tiled) fams.push_back("attention_prefill");
     if (f.decode_attention_tc && tiled && group <= 16 && !bias_ && position_ && gate_name_.empty() && q_norm_name_.empty())
@@ -422,7 +421,7 @@ class Attention : public Mixer {
     // a gate per channel is applied behind the attention kernel, whichever it is
     const float *channel_gate = gate_per_channel_ ? gate : nullptr;
     if (gate_per_channel_) gate = nullptr;
-    if (ctx.dtype == DType::BF16 && plain_ && sink_ == 0) {
+    if (ctx.dtype == DType::BF16 && plain_) {
       if (ctx.decode_only && f.decode_attention && kernels::available("attention_decode") &&
           kernels::attention_decode_supported(d_, group)) {
         // enough CTAs to fill the GPU about eight times over at the longest length, runs of at
@@ -442,19 +441,20 @@ class Attention : public Mixer {
         }
         kernels::attention_decode(q, out, cache->k, cache->v, ctx.tok_pos, cache->page_table, cache->table_width, n_heads_, n_kv_,
                                   d_, cache->page_size, chunk, n_splits, window_, block_, scale_, ws_o, ws_ml, gate, qkv.ld,
-                                  ctx.stream);
+                                  ctx.stream, sink_);
         gate = nullptr;                 // applied
         done = true;
       } else if (f.prefill_attention_tc && (d_ == 64 || d_ == 128) && kernels::available("attention_prefill_tc") &&
                  kernels::attention_prefill_tc_supported(d_, cache->page_size)) {
         kernels::attention_prefill_tc(q, out, cache->k, cache->v, cache->n_pages, ctx.seq_start, ctx.seq_past, cache->page_table,
                                       cache->table_width, ctx.n_seqs, ctx.max_q_len, n_heads_, n_kv_, d_, cache->page_size, window_,
-                                      block_, scale_, ctx.tc_status, ctx.stream);
+                                      block_, scale_, ctx.tc_status, ctx.stream, sink_);
         done = true;
       } else if (f.prefill_attention && kernels::available("attention_prefill") &&
                  kernels::attention_prefill_supported(d_, cache->page_size)) {
         kernels::attention_prefill(q, out, cache->k, cache->v, ctx.seq_start, ctx.seq_past, cache->page_table, cache->table_width,
-                                   ctx.n_seqs, ctx.max_q_len, n_heads_, n_kv_, d_, cache->page_size, window_, block_, scale_, ctx.stream);
+                                   ctx.n_seqs, ctx.max_q_len, n_heads_, n_kv_, d_, cache->page_size, window_, block_, scale_, ctx.stream,
+                                   sink_);
         done = true;
       }
       if (done && gate) kernels::head_gate(out, gate, qkv.ld, n_heads_, dv_, ctx.stream);
