@@ -362,6 +362,111 @@ COMPARE_SIZES = {
 }
 
 
+# ---------------------------------------------------------------- Sesuzen beside Llama at equal sizes
+def sesuzen_config(hidden, runs, heads, kv, dim, ff, vocab, window, keep, moe=None, taps=4, rank=64):
+    """A Sesuzen model of `runs` layer runs: a delta-rule layer and an attention layer (a window of `window`
+    positions that keeps the first `keep`) in a loop that repeats as often as the runs ask for.  `moe` =
+    (experts, top, expert ff) puts a routed feed-forward into the attention layers."""
+    attention = dict(heads=heads, kv_heads=kv, dim=dim, vdim=dim, scale=dim ** -0.5, mask=dict(size=window, keep_first=keep))
+    delta = dict(heads=hidden // dim, dim=dim, rank=rank)
+    dense = dict(kind="dense", ff=ff)
+    routed = dense if moe is None else dict(kind="moe", router=dict(experts=moe[0], top=moe[1]), expert=dict(ff=moe[2]))
+    return dict(architecture="Sesuzen", vocab=vocab, width=hidden, max_positions=CONTEXT, norm=dict(eps=1e-5), canon=dict(taps=taps),
+                logit_softcap=30.0, layers=[dict(type="general_delta", mixer=delta, mlp=dense), dict(type="attention", mixer=attention, mlp=routed)],
+                loop=dict(start=0, stop=2, times=max(1, runs // 2)))
+
+
+def sesuzen_numbers(c, batch):
+    """(bytes a decode step reads at `batch` apart from the cache, cache bytes per visible token, bytes of recurrent
+    state a step reads and writes per sequence, prefill flops of T tokens with one wanted row)."""
+    H, V = c["width"], c["vocab"]
+    loop = c["loop"]
+    runs = list(range(loop["start"])) + list(range(loop["start"], loop["stop"])) * loop["times"] + list(range(loop["stop"], len(c["layers"])))
+
+    def layer_mats(L, tokens):
+        """(matrix values every token uses, matrix values the step reads) of one layer"""
+        m, f = L["mixer"], L["mlp"]
+        if L["type"] == "attention":
+            mix = H * (m["heads"] * m["dim"] + m["kv_heads"] * (m["dim"] + m["vdim"]) + m["heads"] * m["vdim"]) + m["heads"] * m["vdim"] * H
+        else:
+            W = m["heads"] * m["dim"]
+            mix = 6 * H * W + m["rank"] * (H + 2 * W)             # r, k, v, g, a, o; the low-rank pair (the second in 32-bit)
+        if f["kind"] == "dense":
+            return mix + 2 * H * f["ff"], mix + 2 * H * f["ff"]
+        E, top, eff = f["router"]["experts"], f["router"]["top"], f["expert"]["ff"]
+        return mix + H * E + 3 * H * top * eff, mix + H * E + 3 * H * min(E, tokens * top) * eff
+
+    weight_bytes = 2 * (sum(layer_mats(c["layers"][i], batch)[1] for i in runs) + V * H)
+    att = [c["layers"][i]["mixer"] for i in runs if c["layers"][i]["type"] == "attention"]
+    dl = [c["layers"][i]["mixer"] for i in runs if c["layers"][i]["type"] != "attention"]
+    kv_per_token = sum(2 * m["kv_heads"] * (m["dim"] + m["vdim"]) for m in att)
+    state_bytes = sum(2 * 4 * m["heads"] * m["dim"] * m["dim"] for m in dl)      # read and written, 32-bit
+
+    def prefill_flops(T):
+        lin = 2 * T * sum(layer_mats(c["layers"][i], T)[0] for i in runs)
+        a = 0
+        for m in att:
+            w, k = m["mask"]["size"], m["mask"]["keep_first"]
+            seen = sum(min(i + 1, w) + max(0, min(k, i + 1 - w)) for i in range(T))
+            a += 2 * m["heads"] * (m["dim"] + m["vdim"]) * seen
+        rec = sum(10 * m["heads"] * m["dim"] * m["dim"] * T for m in dl)       # decay, removal, outer product, read-out per column
+        return lin + a + rec + 2 * V * H
+    return weight_bytes, kv_per_token, state_bytes, prefill_flops
+
+
+SESUZEN_SIZES = {
+    # name: (hidden, layer runs, heads, kv heads, head size, feed-forward, vocabulary, window, kept first, routed)
+    "2k": (2048, 8, 32, 8, 64, 8192, 32000, 1024, 4, None),
+    "4k": (4096, 4, 32, 8, 128, 14336, 32000, 1024, 4, None),
+    "2k-routed": (2048, 8, 32, 8, 64, 8192, 32000, 1024, 4, (32, 4, 2048)),
+}
+
+
+def run_compare_sesuzen(args):
+    """Prefill and decode of Sesuzen beside Llama, both with random weights, at equal hidden size, layer runs, heads,
+    head size and vocabulary; the feed-forward has two matrices of the width Llama's three have (with experts: the
+    chosen ones' three): one JSON line per size and model."""
+    import torch
+    from libllm_b200 import Model
+    pk = peaks()
+    names = [n for n in SESUZEN_SIZES if not args.sizes or n in args.sizes.split(",")]
+    for name in names:
+        hidden, runs, heads, kv, dim, ff, vocab, window, keep, routed = SESUZEN_SIZES[name]
+        llama = dict(LLAMA_1B, num_hidden_layers=runs, hidden_size=hidden, num_attention_heads=heads, num_key_value_heads=kv,
+                     head_dim=dim, intermediate_size=ff, vocab_size=vocab, tie_word_embeddings=False, rope_scaling=None)
+        zen = sesuzen_config(hidden, runs, heads, kv, dim, ff, vocab, window, keep, routed)
+        only = getattr(args, "model", None)
+        for label, cfg in (("llama", llama), ("sesuzen", zen)):
+            if only and only != label:
+                continue
+            state_bytes = 0
+            if label == "llama":
+                wbytes, kv_per_tok, flops_fn = model_numbers(cfg)
+                flops = flops_fn(PROMPT)
+            else:
+                wbytes, kv_per_tok, state_bytes, zen_flops = sesuzen_numbers(cfg, args.batch)
+                flops = zen_flops(PROMPT)
+            model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=args.batch * CONTEXT, max_seq_len=CONTEXT)
+            pre = prefill_rate(model, vocab, lambda T: flops, pk["bf16_tflops"])
+            rate, ms, ctx_len, launches = decode_rate(model, args.batch, args.steps, args.warmup, vocab)
+            seen = ctx_len if label == "llama" else min(ctx_len, window + keep)
+            step_bytes = wbytes + args.batch * (seen * kv_per_tok + state_bytes)
+            print(json.dumps({"compare": name, "model": label, "batch": args.batch, "prompt": PROMPT,
+                              "config": {"hidden": hidden, "layer_runs": runs, "heads": heads, "kv_heads": kv, "head_dim": dim, "ff": ff,
+                                         "vocab": vocab, "window": window if label == "sesuzen" else None,
+                                         "kept_first": keep if label == "sesuzen" else None, "routed": routed if label == "sesuzen" else None},
+                              "prefill": {"ms": round(pre["ms"], 3), "tok_s": round(pre["value"], 1), "tflop": round(flops / 1e12, 3),
+                                          "frac_of_gemm_peak": round(pre["frac"], 4)},
+                              "decode": {"tok_s": round(rate, 1), "ms_per_step": round(ms, 4), "launches_per_step": launches,
+                                         "step_gb": round(step_bytes / 1e9, 3),
+                                         "hbm_frac": round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)},
+                              "peaks": pk["source"]}), flush=True)
+            model.engine.close()
+            del model
+            torch.cuda.empty_cache()
+    return 0
+
+
 def run_compare(args):
     """Prefill and decode of Sinezen beside Llama, both with random weights, at equal hidden size, layer
     runs, heads, head size, feed-forward width (with experts: equal matrix values used per token) and
@@ -476,8 +581,9 @@ def main():
                     help="1b: the benchmark line (default); 3b, 8b: the larger workloads, a line of their own")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run one part only and print a short line (for profiling; not a bench record)")
-    ap.add_argument("--compare", choices=["sinezen"], default=None,
-                    help="Sinezen beside Llama at equal sizes: prefill and decode, a line per size and model (not a bench record)")
+    ap.add_argument("--compare", choices=["sinezen", "sesuzen"], default=None,
+                    help="Sinezen or Sesuzen beside Llama at equal sizes: prefill and decode, a line per size and model (not a bench record)")
+    ap.add_argument("--model", choices=["llama", "sesuzen"], default=None, help="with --compare sesuzen: one of the two models only")
     ap.add_argument("--sizes", default=None, help="with --compare: which of the sizes (2k, 4k, 2k-routed), with commas")
     ap.add_argument("--prompt-len", type=int, default=None,
                     help="with --only: prompts of this many tokens instead of 2048 (the context grows to fit)")
@@ -495,6 +601,8 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.compare == "sesuzen":
+        return run_compare_sesuzen(args)
     if args.compare:
         return run_compare(args)
     if args.workload != "1b":
