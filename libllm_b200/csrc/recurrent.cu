@@ -117,118 +117,199 @@ LLM_EXPORT int llm_causal_conv(int dtype, const void *h, long long ldh, void *ou
 //   decay   w = exp(-decay_scale * sigmoid(w0 + W2 tanh(x1)))       x1 = the low-rank projection
 //   unit    u = k / sqrt(sum(k^2) + key_eps)
 //   removal b = sigmoid(a + a_bias) * u
-// prep [tokens, heads, 3, d]: w, b, u.  One warp per (token, head); sums over the head in lane
-// order then the shuffle tree, whatever the launch.
-__global__ void __launch_bounds__(128)
+// prep [tokens, heads, 3, d]: w, b, u.  A CTA takes one head and a run of tokens, a warp one token
+// at a time: the head's rows of W2 ([d, rank], each row padded by one value so that the lanes'
+// reads fall on different banks) lie in shared memory when they fit, tanh(x1) is taken once per
+// token and warp.  Sums over the head run in lane order then the shuffle tree, whatever the launch.
+constexpr int DP_WARPS = 4;
+constexpr int DP_TOKENS = 32;                        // tokens of a CTA
+
+__global__ void __launch_bounds__(DP_WARPS * 32)
 delta_prepare_kernel(const float *__restrict__ proj, long long ld, int off_k, int off_a, int off_x1, int rank,
                      const float *__restrict__ w2, const float *__restrict__ w0, const float *__restrict__ a_bias,
-                     float decay_scale, float key_eps, int n_tokens, int n_heads, int d, float *__restrict__ prep) {
+                     float decay_scale, float key_eps, int n_tokens, int n_heads, int d, int w2_shared,
+                     float *__restrict__ prep) {
+  extern __shared__ float dp_smem[];                 // tanh(x1) [warps][rank], then W2's rows of the head [d][rank + 1]
   grid_dependents_launch();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int hd = blockIdx.y;
+  float *th = dp_smem + warp * rank;
+  float *w2s = dp_smem + DP_WARPS * rank;
+  const float *w2h = w2 + (size_t)hd * d * rank;
+  if (w2_shared)                                     // weights: nothing of the step is read yet
+    for (int i = threadIdx.x; i < d * rank; i += DP_WARPS * 32) w2s[(i / rank) * (rank + 1) + i % rank] = w2h[i];
   grid_dependency_wait();
-  const int lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (item >= (long long)n_tokens * n_heads) return;
-  const int t = (int)(item / n_heads), hd = (int)(item - (long long)t * n_heads);
-  const float *row = proj + (size_t)t * ld;
-  const float *k = row + off_k + (size_t)hd * d;
-  float ss = 0.f;
-  for (int i = lane; i < d; i += 32) ss = fmaf(k[i], k[i], ss);
-  ss = warp_sum(ss);
-  const float inv = 1.f / sqrtf(ss + key_eps);
-  float *o = prep + (size_t)item * 3 * d;
-  for (int i = lane; i < d; i += 32) {
-    const int ch = hd * d + i;
-    float z = w0[ch];
-    const float *w2r = w2 + (size_t)ch * rank;
-    for (int q = 0; q < rank; ++q) z = fmaf(w2r[q], tanhf(row[off_x1 + q]), z);
-    const float u = k[i] * inv;
-    const float a = 1.f / (1.f + expf(-(row[off_a + ch] + a_bias[ch])));
-    o[i] = expf(-decay_scale / (1.f + expf(-z)));
-    o[d + i] = a * u;
-    o[2 * d + i] = u;
+  __syncthreads();
+  const int t1 = min(n_tokens, (int)(blockIdx.x + 1) * DP_TOKENS);
+  for (int t = blockIdx.x * DP_TOKENS + warp; t < t1; t += DP_WARPS) {
+    const float *row = proj + (size_t)t * ld;
+    const float *k = row + off_k + (size_t)hd * d;
+    __syncwarp();
+    for (int q = lane; q < rank; q += 32) th[q] = tanhf(row[off_x1 + q]);
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) ss = fmaf(k[i], k[i], ss);
+    ss = warp_sum(ss);
+    __syncwarp();
+    const float inv = 1.f / sqrtf(ss + key_eps);
+    float *o = prep + ((size_t)t * n_heads + hd) * 3 * d;
+    for (int i = lane; i < d; i += 32) {
+      const int ch = hd * d + i;
+      float z = w0[ch];
+      if (w2_shared) {
+        const float *w2r = w2s + i * (rank + 1);
+        for (int q = 0; q < rank; ++q) z = fmaf(w2r[q], th[q], z);
+      } else {
+        const float *w2r = w2h + (size_t)i * rank;
+        for (int q = 0; q < rank; ++q) z = fmaf(w2r[q], th[q], z);
+      }
+      const float u = k[i] * inv;
+      const float a = 1.f / (1.f + expf(-(row[off_a + ch] + a_bias[ch])));
+      o[i] = expf(-decay_scale / (1.f + expf(-z)));
+      o[d + i] = a * u;
+      o[2 * d + i] = u;
+    }
   }
 }
 
 // ---------------------------------------------------------------- the delta rule: the recurrence
 // Per head, state S [d keys x d values]:  S <- diag(w) S - b (u^T S) + k v^T  (both terms read the
-// old S), then o = S^T r.  A column of S never meets another column, so a thread (or LANES
-// neighbouring lanes, each with d / LANES of the rows) owns column j for the whole step and walks
-// the sequence's tokens in order; the token's vectors are staged in shared memory, the next token's
-// loads issued before this token's arithmetic.  state[slot][head][j][i] (a column's rows together).
+// old S), then o = S^T r.  A column of S never meets another column, so LANES neighbouring lanes,
+// each with d / LANES of its rows in registers, own column j for the whole step and walk the
+// sequence's tokens in order.  The tokens' vectors (w, b, u from the preparation, k and r from the
+// product's rows, the CTA's columns of v) come through a ring of DR_STAGES tokens in shared memory,
+// filled by asynchronous copies that run that many tokens ahead of the arithmetic, so that a token
+// costs its arithmetic and half a barrier, not a trip to memory.  Sums run over four partial sums in
+// a fixed order, then the lanes' shuffle tree.  state[slot][head][j][i] (a column's rows together).
 constexpr int DR_THREADS = 64;
+constexpr int DR_STAGES = 8;
 
-template <int DMAX, int LANES>
+__device__ __forceinline__ void cp_async4(void *smem, const void *gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async16_cg(void *smem, const void *gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int DMAX, int LANES, bool VEC>
 __global__ void __launch_bounds__(DR_THREADS)
 delta_rule_kernel(const float *__restrict__ proj, long long ld, int off_r, int off_k, int off_v,
                   const float *__restrict__ prep, float *__restrict__ state, float *__restrict__ out, long long ldo,
                   const int *__restrict__ seq_start, const int *__restrict__ seq_slot, int n_heads, int d) {
   constexpr int ROWS = DMAX / LANES;                 // rows of a column held by one thread
   constexpr int COLS = DR_THREADS / LANES;           // columns of a CTA
-  __shared__ __align__(16) float vec[2][5][DMAX];    // w, b, u, k, r of a token, two tokens in turn
-  __shared__ float vcol[2][COLS];
+  constexpr int PAD = ROWS + 4;                      // a lane's share of a vector, padded: the lanes' loads fall on different banks
+  constexpr int VLEN = LANES * PAD;
+  constexpr int SLOT = 5 * VLEN + COLS;              // floats of one token in the ring: w, b, u, k, r, then the CTA's columns of v
+  constexpr int UNIT = VEC ? 4 : 1;                  // floats to a copy
+  constexpr int PER = (5 * DMAX / UNIT + COLS / UNIT + DR_THREADS - 1) / DR_THREADS;   // copies of a thread per token
+  __shared__ __align__(16) float ring[DR_STAGES][SLOT];
   grid_dependents_launch();
   grid_dependency_wait();
   const int b = blockIdx.x, hd = blockIdx.y;
   const int tid = threadIdx.x, sub = tid % LANES, col = tid / LANES;
-  const int j = blockIdx.z * COLS + col;
+  const int j0 = blockIdx.z * COLS, j = j0 + col;
   const int start = seq_start[b], n = seq_start[b + 1] - start;
   const bool live = j < d;
   float S[ROWS];
   float *sp = state + (((size_t)seq_slot[b] * n_heads + hd) * d + (live ? j : 0)) * d + sub * ROWS;
 #pragma unroll
   for (int i = 0; i < ROWS; ++i) S[i] = (live && sub * ROWS + i < d) ? sp[i] : 0.f;
+  // rows beyond d of a lane's share are never copied: they stay zero, and so do the state's rows there
+  for (int i = tid; i < DR_STAGES * SLOT; i += DR_THREADS) (&ring[0][0])[i] = 0.f;
 
-  // what this thread stages for a token: elements tid, tid + DR_THREADS, ... of the five vectors
-  constexpr int PER = (5 * DMAX + DR_THREADS - 1) / DR_THREADS;
-  float stage[PER], stage_v = 0.f;
+  // This thread's copies of a token, worked out once: where from (an offset into the token's prepared vectors, or
+  // into its row of the product, marked by bit 30) and where to (element i of a vector lies at (i / ROWS) * PAD + i % ROWS).
+  int from[PER], to[PER];
+  {
+    const int per_vec = d / UNIT, n_v = (min(COLS, d - j0) + UNIT - 1) / UNIT;
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+      const int idx = tid + e * DR_THREADS;
+      from[e] = to[e] = -1;
+      if (idx < 5 * per_vec) {
+        const int which = idx / per_vec, i = (idx - which * per_vec) * UNIT;
+        from[e] = which < 3 ? which * d + i : ((which == 3 ? off_k : off_r) + hd * d + i) | (1 << 30);
+        to[e] = which * VLEN + (i / ROWS) * PAD + i % ROWS;
+      } else if (idx - 5 * per_vec < n_v) {
+        const int i = (idx - 5 * per_vec) * UNIT;
+        from[e] = (off_v + hd * d + j0 + i) | (1 << 30);
+        to[e] = 5 * VLEN + i;
+      }
+    }
+  }
+  __syncthreads();
   auto fetch = [&](int t) {
+    float *dst = ring[t % DR_STAGES];
     const float *row = proj + (size_t)(start + t) * ld;
     const float *pr = prep + ((size_t)(start + t) * n_heads + hd) * 3 * d;
 #pragma unroll
-    for (int e = 0; e < PER; ++e) {
-      const int idx = tid + e * DR_THREADS, which = idx / DMAX, i = idx - which * DMAX;
-      float v = 0.f;
-      if (which < 5 && i < d) v = which < 3 ? pr[which * d + i] : row[(which == 3 ? off_k : off_r) + hd * d + i];
-      stage[e] = v;
-    }
-    if (tid < COLS) stage_v = blockIdx.z * COLS + tid < d ? row[off_v + hd * d + blockIdx.z * COLS + tid] : 0.f;
+    for (int e = 0; e < PER; ++e)
+      if (to[e] >= 0) {
+        const float *src = (from[e] & (1 << 30)) ? row + (from[e] & ~(1 << 30)) : pr + from[e];
+        if (VEC) cp_async16_cg(dst + to[e], src);
+        else cp_async4(dst + to[e], src);
+      }
   };
-  auto put = [&](int buf) {
+  auto token = [&](int t) {
+    const float *slot = ring[t % DR_STAGES];
+    const float *w = slot + sub * PAD, *bb = w + VLEN, *u = bb + VLEN, *k = u + VLEN, *r = k + VLEN;
+    const float v = slot[5 * VLEN + col];
+    // a lane's share of every vector starts on 16 bytes (PAD and VLEN are multiples of 4): four values to a load
+    const float4 *w4 = reinterpret_cast<const float4 *>(w), *b4 = reinterpret_cast<const float4 *>(bb);
+    const float4 *u4 = reinterpret_cast<const float4 *>(u), *k4 = reinterpret_cast<const float4 *>(k);
+    const float4 *r4 = reinterpret_cast<const float4 *>(r);
+    float p4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int e = 0; e < PER; ++e) {
-      const int idx = tid + e * DR_THREADS, which = idx / DMAX, i = idx - which * DMAX;
-      if (which < 5) vec[buf][which][i] = stage[e];
+    for (int i = 0; i < ROWS / 4; ++i) {
+      const float4 uu = u4[i];
+      p4[0] = fmaf(uu.x, S[4 * i], p4[0]);
+      p4[1] = fmaf(uu.y, S[4 * i + 1], p4[1]);
+      p4[2] = fmaf(uu.z, S[4 * i + 2], p4[2]);
+      p4[3] = fmaf(uu.w, S[4 * i + 3], p4[3]);
     }
-    if (tid < COLS) vcol[buf][tid] = stage_v;
-  };
-  if (n > 0) {
-    fetch(0);
-    put(0);
-  }
-  __syncthreads();
-  for (int t = 0; t < n; ++t) {
-    const int buf = t & 1;
-    if (t + 1 < n) fetch(t + 1);
-    const float *w = vec[buf][0] + sub * ROWS, *bb = vec[buf][1] + sub * ROWS, *u = vec[buf][2] + sub * ROWS;
-    const float *k = vec[buf][3] + sub * ROWS, *r = vec[buf][4] + sub * ROWS;
-    const float v = vcol[buf][col];
-    float us = 0.f;
-#pragma unroll
-    for (int i = 0; i < ROWS; ++i) us = fmaf(u[i], S[i], us);
+    float us = (p4[0] + p4[1]) + (p4[2] + p4[3]);
 #pragma unroll
     for (int o = 1; o < LANES; o <<= 1) us += __shfl_xor_sync(0xffffffffu, us, o);
-    float acc = 0.f;
+    float a4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int i = 0; i < ROWS; ++i) {
-      S[i] = fmaf(w[i], S[i], fmaf(k[i], v, -bb[i] * us));
-      acc = fmaf(S[i], r[i], acc);
+    for (int i = 0; i < ROWS / 4; ++i) {
+      const float4 ww = w4[i], bq = b4[i], kk = k4[i], rr = r4[i];
+      S[4 * i] = fmaf(ww.x, S[4 * i], fmaf(kk.x, v, -bq.x * us));
+      S[4 * i + 1] = fmaf(ww.y, S[4 * i + 1], fmaf(kk.y, v, -bq.y * us));
+      S[4 * i + 2] = fmaf(ww.z, S[4 * i + 2], fmaf(kk.z, v, -bq.z * us));
+      S[4 * i + 3] = fmaf(ww.w, S[4 * i + 3], fmaf(kk.w, v, -bq.w * us));
+      a4[0] = fmaf(S[4 * i], rr.x, a4[0]);
+      a4[1] = fmaf(S[4 * i + 1], rr.y, a4[1]);
+      a4[2] = fmaf(S[4 * i + 2], rr.z, a4[2]);
+      a4[3] = fmaf(S[4 * i + 3], rr.w, a4[3]);
     }
+    float acc = (a4[0] + a4[1]) + (a4[2] + a4[3]);
 #pragma unroll
     for (int o = 1; o < LANES; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if (live && sub == 0) out[(size_t)(start + t) * ldo + (size_t)hd * d + j] = acc;
-    if (t + 1 < n) put(buf ^ 1);
+  };
+  // Tokens go through the ring in pairs: a group of copies is a pair, DR_STAGES / 2 - 1 pairs are in flight, and a
+  // barrier stands before every pair (its copies have arrived for everyone, and everyone is done with the pair
+  // whose place the next copies take).
+  constexpr int PAIRS = DR_STAGES / 2;
+  const int n_pairs = (n + 1) / 2;
+  auto fetch_pair = [&](int p) {
+    if (2 * p < n) fetch(2 * p);
+    if (2 * p + 1 < n) fetch(2 * p + 1);
+    cp_async_commit_group();
+  };
+  for (int p = 0; p < PAIRS - 1; ++p) fetch_pair(p);
+  for (int p = 0; p < n_pairs; ++p) {
+    cp_async_wait_group<PAIRS - 2>();
     __syncthreads();
+    fetch_pair(p + PAIRS - 1);
+    token(2 * p);
+    if (2 * p + 1 < n) token(2 * p + 1);
   }
+  cp_async_wait_group<0>();
   if (live)
 #pragma unroll
     for (int i = 0; i < ROWS; ++i)
@@ -243,18 +324,33 @@ LLM_EXPORT int llm_delta_rule(const float *proj, long long ld, int off_r, int of
   LLM_REQUIRE(n_tokens > 0 && n_seqs > 0 && n_heads > 0 && d > 0 && rank > 0, "delta_rule: bad sizes");
   LLM_REQUIRE(d <= 256, "delta_rule: heads of %d channels are not supported (up to 256)", d);
   LLM_REQUIRE(n_heads <= 65535 && n_seqs < 2147483647, "delta_rule: too many heads or sequences");
-  const long long items = (long long)n_tokens * n_heads;
-  llm_launch(delta_prepare_kernel, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, proj, ld, off_k, off_a, off_x1, rank, w2,
-             w0, a_bias, decay_scale, key_eps, n_tokens, n_heads, d, prep);
-  LLM_CHECK_LAUNCH("delta_prepare");
-#define DR_GO(DMAX, LANES)                                                                                              \
-  llm_launch(delta_rule_kernel<DMAX, LANES>, dim3(n_seqs, n_heads, (d + DR_THREADS / LANES - 1) / (DR_THREADS / LANES)), \
+  {
+    const size_t with_w2 = ((size_t)DP_WARPS * rank + (size_t)d * (rank + 1)) * sizeof(float);
+    const int w2_shared = with_w2 <= 96 * 1024;
+    const size_t smem = w2_shared ? with_w2 : (size_t)DP_WARPS * rank * sizeof(float);
+    LLM_REQUIRE(smem <= 96 * 1024, "delta_rule: a decay input of rank %d is not supported", rank);
+    LLM_CHECK_CUDA(llm_allow_smem(delta_prepare_kernel, smem), "delta_prepare attribute");
+    llm_launch(delta_prepare_kernel, dim3((unsigned)((n_tokens + DP_TOKENS - 1) / DP_TOKENS), n_heads), dim3(DP_WARPS * 32), smem, stream,
+               proj, ld, off_k, off_a, off_x1, rank, w2, w0, a_bias, decay_scale, key_eps, n_tokens, n_heads, d, w2_shared, prep);
+    LLM_CHECK_LAUNCH("delta_prepare");
+  }
+  // 16-byte copies where every vector starts on such a boundary
+  const bool vec16 = d % 4 == 0 && ld % 4 == 0 && off_r % 4 == 0 && off_k % 4 == 0 && off_v % 4 == 0 && (uintptr_t)proj % 16 == 0 &&
+                     (uintptr_t)prep % 16 == 0;
+#define DR_GO2(DMAX, LANES, VEC)                                                                                        \
+  llm_launch(delta_rule_kernel<DMAX, LANES, VEC>, dim3(n_seqs, n_heads, (d + DR_THREADS / LANES - 1) / (DR_THREADS / LANES)), \
              dim3(DR_THREADS), 0, stream, proj, ld, off_r, off_k, off_v, (const float *)prep, state, out, ldo, seq_start, \
              seq_slot, n_heads, d)
+#define DR_GO(DMAX, LANES)              \
+  do {                                  \
+    if (vec16) DR_GO2(DMAX, LANES, true); \
+    else DR_GO2(DMAX, LANES, false);    \
+  } while (0)
   if (d <= 32) DR_GO(32, 2);
   else if (d <= 64) DR_GO(64, 4);
   else if (d <= 128) DR_GO(128, 4);
   else DR_GO(256, 8);
+#undef DR_GO2
 #undef DR_GO
   LLM_CHECK_LAUNCH("delta_rule");
   return LLM_OK;
