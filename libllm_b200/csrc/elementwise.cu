@@ -321,10 +321,112 @@ add_layernorm_kernel(float *__restrict__ resid, const TD *__restrict__ delta, in
     o[c] = from_float<TO>((row_buf[c] - mean) * inv * weight[c] + (bias ? bias[c] : 0.f));
 }
 
+// The same with the row in registers, four values to a load (widths that are multiples of 4, up to 8,192; up
+// to MAXP parts, whose loads are all issued before any is used).  The sums' order within a thread differs from
+// the general kernel's only in which thread owns which columns; a row's result does not depend on the launch.
+template <typename TD, typename TO, int THREADS, int VPT, int MAXP>
+__global__ void __launch_bounds__(THREADS)
+add_layernorm_vec_kernel(float *__restrict__ resid, const TD *__restrict__ delta, int n_parts, size_t part_stride,
+                         const float *__restrict__ weight, const float *__restrict__ bias, float eps, TO *__restrict__ out,
+                         const int *__restrict__ rows, int hidden) {
+  __shared__ float scratch[THREADS / 32 + 1];
+  grid_dependents_launch();
+  const int i = blockIdx.x;
+  const int n4 = hidden / 4;
+  float4 v[VPT], w[VPT], b[VPT], d[VPT][MAXP];
+  if (out) {                             // the norm's weight and bias do not depend on the kernel before
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int c4 = threadIdx.x + j * THREADS;
+      if (c4 < n4) {
+        w[j] = ld4(weight + 4 * c4);
+        b[j] = bias ? ld4(bias + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+  }
+  grid_dependency_wait();
+  const int r = rows ? rows[i] : i;
+  float *x = resid + (size_t)r * hidden;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int c4 = threadIdx.x + j * THREADS;
+    if (c4 < n4) {
+      v[j] = ld4(x + 4 * c4);
+#pragma unroll
+      for (int p = 0; p < MAXP; ++p)
+        if (p < n_parts) d[j][p] = ld4(delta + p * part_stride + (size_t)r * hidden + 4 * c4);
+    }
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int c4 = threadIdx.x + j * THREADS;
+    if (c4 < n4) {
+#pragma unroll
+      for (int p = 0; p < MAXP; ++p)
+        if (p < n_parts) {
+          v[j].x += d[j][p].x;
+          v[j].y += d[j][p].y;
+          v[j].z += d[j][p].z;
+          v[j].w += d[j][p].w;
+        }
+      if (!rows && n_parts > 0) st4(x + 4 * c4, v[j]);
+      sum += v[j].x;
+      sum += v[j].y;
+      sum += v[j].z;
+      sum += v[j].w;
+    }
+  }
+  if (!out) return;
+  const float mean = block_sum<THREADS>(sum, scratch) / (float)hidden;
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int c4 = threadIdx.x + j * THREADS;
+    if (c4 < n4) {
+      v[j] = make_float4(v[j].x - mean, v[j].y - mean, v[j].z - mean, v[j].w - mean);
+      ss = fmaf(v[j].x, v[j].x, ss);
+      ss = fmaf(v[j].y, v[j].y, ss);
+      ss = fmaf(v[j].z, v[j].z, ss);
+      ss = fmaf(v[j].w, v[j].w, ss);
+    }
+  }
+  const float var = block_sum<THREADS>(ss, scratch) / (float)hidden;
+  const float inv = 1.f / sqrtf(var + eps);
+  TO *o = out + (size_t)i * hidden;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int c4 = threadIdx.x + j * THREADS;
+    if (c4 < n4)
+      st4(o + 4 * c4, make_float4(v[j].x * inv * w[j].x + b[j].x, v[j].y * inv * w[j].y + b[j].y, v[j].z * inv * w[j].z + b[j].z,
+                                  v[j].w * inv * w[j].w + b[j].w));
+  }
+}
+
 template <typename TD, typename TO>
 static int launch_add_layernorm(float *resid, const void *delta, int n_parts, size_t part_stride, const float *weight,
                                 const float *bias, float eps, void *out, const int *rows, int n_rows, int hidden,
                                 cudaStream_t stream) {
+  const bool aligned = hidden % 4 == 0 && (uintptr_t)resid % 16 == 0 && (uintptr_t)delta % 16 == 0 && (uintptr_t)weight % 16 == 0 &&
+                       (uintptr_t)bias % 16 == 0 && (uintptr_t)out % 16 == 0 && part_stride % 4 == 0;
+  if (aligned && hidden <= 8192 && n_parts <= 4) {
+#define ADDLN_GO(T_, V_, MAXP)                                                                            \
+  llm_launch(add_layernorm_vec_kernel<TD, TO, T_, V_, MAXP>, n_rows, T_, 0, stream, resid, (const TD *)delta, n_parts, part_stride, \
+             weight, bias, eps, (TO *)out, rows, hidden)
+#define ADDLN_SIZE(MAXP)                                    \
+  do {                                                      \
+    if (hidden <= 512) ADDLN_GO(128, 1, MAXP);              \
+    else if (hidden <= 2048) ADDLN_GO(512, 1, MAXP);        \
+    else if (hidden <= 4096) ADDLN_GO(1024, 1, MAXP);       \
+    else ADDLN_GO(1024, 2, MAXP);                           \
+  } while (0)
+    if (n_parts <= 1) ADDLN_SIZE(1);
+    else ADDLN_SIZE(4);
+#undef ADDLN_SIZE
+#undef ADDLN_GO
+    LLM_CHECK_LAUNCH("add_layernorm");
+    return LLM_OK;
+  }
   const size_t smem = (size_t)hidden * sizeof(float);
   LLM_REQUIRE(smem <= 200 * 1024, "add_layernorm: a row of %d values does not fit shared memory", hidden);
   if (hidden <= 1024) {
@@ -600,10 +702,41 @@ __global__ void head_gate_vec_kernel(T *__restrict__ x, long long ld, const floa
   }
 }
 
+// A gate per channel: x[t, c] *= sigmoid(gate[t * gate_stride + c]), four channels to a thread.
+template <typename T>
+__global__ void channel_gate_vec_kernel(T *__restrict__ x, long long ld, const float *__restrict__ gate, long long gate_stride,
+                                        int width4, size_t total4) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / width4;
+    const int c = (int)(idx - t * width4) * 4;
+    const float4 g = ld4(gate + t * gate_stride + c);
+    T *p = x + t * ld + c;
+    const float4 v = ld4(p);
+    st4(p, make_float4(v.x / (1.f + expf(-g.x)), v.y / (1.f + expf(-g.y)), v.z / (1.f + expf(-g.z)), v.w / (1.f + expf(-g.w))));
+  }
+}
+
 LLM_EXPORT int llm_head_gate(void *x, int dtype, long long ld, const float *gate, long long gate_stride, int n_tokens,
                              int n_heads, int dv, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && dv > 0 && x && gate, "head_gate: bad arguments");
+  if (dv == 1 && n_heads % 4 == 0 && ld % 4 == 0 && gate_stride % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)gate % 16 == 0) {
+    // heads of one channel: a gate per channel
+    const size_t total4 = (size_t)n_tokens * (n_heads / 4);
+    size_t blocks4 = (total4 + 255) / 256;
+    if (blocks4 > (size_t)sm_count() * 32) blocks4 = (size_t)sm_count() * 32;
+    if (dtype == LLM_F32)
+      llm_launch(channel_gate_vec_kernel<float>, dim3((unsigned)blocks4), dim3(256), 0, stream, (float *)x, ld, gate, gate_stride,
+                 n_heads / 4, total4);
+    else if (dtype == LLM_BF16)
+      llm_launch(channel_gate_vec_kernel<__nv_bfloat16>, dim3((unsigned)blocks4), dim3(256), 0, stream, (__nv_bfloat16 *)x, ld, gate,
+                 gate_stride, n_heads / 4, total4);
+    else LLM_FAIL("head_gate: unknown dtype %d", dtype);
+    LLM_CHECK_LAUNCH("head_gate");
+    return LLM_OK;
+  }
   if (dv % 4 == 0 && ld % 4 == 0 && (uintptr_t)x % 16 == 0) {
     const size_t total4 = (size_t)n_tokens * n_heads * (dv / 4);
     size_t blocks4 = (total4 + 255) / 256;

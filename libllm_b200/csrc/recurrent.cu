@@ -41,21 +41,74 @@ __device__ __forceinline__ float conv_row(const float (&w)[CONV_MAX_TAPS], const
   return pick(vals, taps - 1) + s;
 }
 
-template <typename T>
+// V channels to a thread: 1, or as many as 16 bytes hold where rows allow such loads.
+template <typename T, int V>
+struct ConvVec {
+  float x[V];
+};
+template <typename T, int V>
+__device__ __forceinline__ ConvVec<T, V> conv_load(const T *p) {
+  ConvVec<T, V> r;
+  if (V == 1) {
+    r.x[0] = to_float(p[0]);
+  } else if (sizeof(T) == 4) {
+    const float4 v = *reinterpret_cast<const float4 *>(p);
+    r.x[0] = v.x, r.x[1] = v.y, r.x[2] = v.z, r.x[3] = v.w;
+  } else {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(p);
+    const __nv_bfloat162 *h2 = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+      const float2 f = __bfloat1622float2(h2[i]);
+      r.x[2 * i] = f.x, r.x[2 * i + 1] = f.y;
+    }
+  }
+  return r;
+}
+template <typename T, int V>
+__device__ __forceinline__ void conv_store(T *p, const ConvVec<T, V> &r) {
+  if (V == 1) {
+    p[0] = from_float<T>(r.x[0]);
+  } else if (sizeof(T) == 4) {
+    *reinterpret_cast<float4 *>(p) = make_float4(r.x[0], r.x[1], r.x[2], r.x[3]);
+  } else {
+    uint4 raw;
+    __nv_bfloat162 *h2 = reinterpret_cast<__nv_bfloat162 *>(&raw);
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) h2[i] = __floats2bfloat162_rn(r.x[2 * i], r.x[2 * i + 1]);
+    *reinterpret_cast<uint4 *>(p) = raw;
+  }
+}
+
+template <typename T, int V>
 __global__ void __launch_bounds__(CONV_THREADS)
 causal_conv_kernel(const T *__restrict__ h, long long ldh, T *__restrict__ out, long long ldo, const float *__restrict__ weight,
                    T *__restrict__ state, const int *__restrict__ tok_seq, const int *__restrict__ tok_pos,
                    const int *__restrict__ seq_start, const int *__restrict__ seq_past, const int *__restrict__ seq_slot,
                    int n_tokens, int width, int taps, int n_chunks, int chunk_rows) {
+  using Vec = ConvVec<T, V>;
   grid_dependents_launch();
-  const int c = blockIdx.x * CONV_THREADS + threadIdx.x;
-  float w[CONV_MAX_TAPS];
+  const int c = (blockIdx.x * CONV_THREADS + threadIdx.x) * V;
+  float w[V][CONV_MAX_TAPS];
 #pragma unroll
-  for (int j = 0; j < CONV_MAX_TAPS; ++j) w[j] = (c < width && j < taps) ? weight[(size_t)c * taps + j] : 0.f;
+  for (int v = 0; v < V; ++v)
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) w[v][j] = (c + v < width && j < taps) ? weight[(size_t)(c + v) * taps + j] : 0.f;
   grid_dependency_wait();
   if (c >= width) return;
   const int keep = taps - 1;
-  float vals[CONV_MAX_TAPS];
+  Vec vals[CONV_MAX_TAPS];
+  auto row_out = [&]() {                              // the same order of operations wherever a row is computed
+    Vec r;
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      float column[CONV_MAX_TAPS];
+#pragma unroll
+      for (int j = 0; j < CONV_MAX_TAPS; ++j) column[j] = vals[j].x[v];
+      r.x[v] = conv_row(w[v], column, taps);
+    }
+    return r;
+  };
   if ((int)blockIdx.y < n_chunks) {
     const int r0 = blockIdx.y * chunk_rows, r1 = min(n_tokens, r0 + chunk_rows);
     for (int row = r0; row < r1; ++row) {
@@ -63,25 +116,34 @@ causal_conv_kernel(const T *__restrict__ h, long long ldh, T *__restrict__ out, 
       if (tok_pos[row] - seq_past[b] < keep) continue;          // the sequence's own CTA computes it
 #pragma unroll
       for (int j = 0; j < CONV_MAX_TAPS; ++j)
-        vals[j] = j < taps ? to_float(h[(size_t)(row - keep + j) * ldh + c]) : 0.f;
-      out[(size_t)row * ldo + c] = from_float<T>(conv_row(w, vals, taps));
+        if (j < taps) vals[j] = conv_load<T, V>(h + (size_t)(row - keep + j) * ldh + c);
+      conv_store<T, V>(out + (size_t)row * ldo + c, row_out());
     }
     return;
   }
   const int b = blockIdx.y - n_chunks;
   const int start = seq_start[b], n = seq_start[b + 1] - start;
   T *st = state + (size_t)seq_slot[b] * keep * width + c;
-  float old[CONV_MAX_TAPS - 1];
+  Vec old[CONV_MAX_TAPS - 1];
 #pragma unroll
-  for (int i = 0; i < CONV_MAX_TAPS - 1; ++i) old[i] = i < keep ? to_float(st[(size_t)i * width]) : 0.f;
+  for (int i = 0; i < CONV_MAX_TAPS - 1; ++i)
+    if (i < keep) old[i] = conv_load<T, V>(st + (size_t)i * width);
   // position (relative to the sequence's length before the step) -> input
-  auto at = [&](int rel) { return rel < 0 ? pick(old, keep + rel) : to_float(h[(size_t)(start + rel) * ldh + c]); };
+  auto at = [&](int rel) {
+    if (rel >= 0) return conv_load<T, V>(h + (size_t)(start + rel) * ldh + c);
+    Vec r = old[0];
+#pragma unroll
+    for (int i = 1; i < CONV_MAX_TAPS - 1; ++i)
+      if (i == keep + rel) r = old[i];
+    return r;
+  };
   for (int i = 0; i < min(n, keep); ++i) {
 #pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; ++j) vals[j] = j < taps ? at(i - keep + j) : 0.f;
-    out[(size_t)(start + i) * ldo + c] = from_float<T>(conv_row(w, vals, taps));
+    for (int j = 0; j < CONV_MAX_TAPS; ++j)
+      if (j < taps) vals[j] = at(i - keep + j);
+    conv_store<T, V>(out + (size_t)(start + i) * ldo + c, row_out());
   }
-  for (int i = 0; i < keep; ++i) st[(size_t)i * width] = from_float<T>(at(n - keep + i));
+  for (int i = 0; i < keep; ++i) conv_store<T, V>(st + (size_t)i * width, at(n - keep + i));
 }
 
 LLM_EXPORT int llm_causal_conv(int dtype, const void *h, long long ldh, void *out, long long ldo, const float *weight, void *state,
@@ -98,15 +160,21 @@ LLM_EXPORT int llm_causal_conv(int dtype, const void *h, long long ldh, void *ou
   const int n_own = taps > 1 ? n_seqs : 0;
   if (n_chunks + n_own == 0) return LLM_OK;
   LLM_REQUIRE(n_chunks + n_own <= 65535, "causal_conv: too many rows for one launch");
-  const dim3 grid((width + CONV_THREADS - 1) / CONV_THREADS, n_chunks + n_own);
-  if (dtype == LLM_F32)
-    llm_launch(causal_conv_kernel<float>, grid, dim3(CONV_THREADS), 0, stream, (const float *)h, ldh, (float *)out, ldo, weight,
-               (float *)state, tok_seq, tok_pos, seq_start, seq_past, seq_slot, n_tokens, width, taps, n_chunks, chunk_rows);
-  else if (dtype == LLM_BF16)
-    llm_launch(causal_conv_kernel<__nv_bfloat16>, grid, dim3(CONV_THREADS), 0, stream, (const __nv_bfloat16 *)h, ldh,
-               (__nv_bfloat16 *)out, ldo, weight, (__nv_bfloat16 *)state, tok_seq, tok_pos, seq_start, seq_past, seq_slot, n_tokens,
-               width, taps, n_chunks, chunk_rows);
+  // 16 bytes of channels to a thread where every row starts on such a boundary
+  const int per = dtype == LLM_F32 ? 4 : 8;
+  const bool vec = width % per == 0 && ldh % per == 0 && ldo % per == 0 && (uintptr_t)h % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+                   (uintptr_t)state % 16 == 0;
+  const int v = vec ? per : 1;
+  const dim3 grid((width + CONV_THREADS * v - 1) / (CONV_THREADS * v), n_chunks + n_own);
+#define CONV_GO(T, V)                                                                                                       \
+  llm_launch(causal_conv_kernel<T, V>, grid, dim3(CONV_THREADS), 0, stream, (const T *)h, ldh, (T *)out, ldo, weight, (T *)state, \
+             tok_seq, tok_pos, seq_start, seq_past, seq_slot, n_tokens, width, taps, n_chunks, chunk_rows)
+  if (dtype == LLM_F32 && vec) CONV_GO(float, 4);
+  else if (dtype == LLM_F32) CONV_GO(float, 1);
+  else if (dtype == LLM_BF16 && vec) CONV_GO(__nv_bfloat16, 8);
+  else if (dtype == LLM_BF16) CONV_GO(__nv_bfloat16, 1);
   else LLM_FAIL("causal_conv: unknown dtype %d", dtype);
+#undef CONV_GO
   LLM_CHECK_LAUNCH("causal_conv");
   return LLM_OK;
 }
@@ -360,7 +428,7 @@ LLM_EXPORT int llm_delta_rule(const float *proj, long long ld, int off_r, int of
 // out[t, h, :] = x[t, h, :] / sqrt(mean(x[t, h, :]^2) + eps) * weight[h, :] * sigmoid(gate[t, h, :])
 // eps < 0: no norm; weight null: none; gate null: none (gate: 32-bit logits, row stride gate_stride).
 // One warp per (token, head).
-template <typename T>
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float *__restrict__ x, long long ldx, const float *__restrict__ weight, const float *__restrict__ gate,
                       long long gate_stride, float eps, int n_tokens, int n_heads, int dv, T *__restrict__ out, long long ldo) {
@@ -371,6 +439,40 @@ head_norm_gate_kernel(const float *__restrict__ x, long long ldx, const float *_
   if (item >= (long long)n_tokens * n_heads) return;
   const int t = (int)(item / n_heads), hd = (int)(item - (long long)t * n_heads);
   const float *xr = x + (size_t)t * ldx + (size_t)hd * dv;
+  const float *wr = weight ? weight + (size_t)hd * dv : nullptr;
+  const float *gr = gate ? gate + (size_t)t * gate_stride + (size_t)hd * dv : nullptr;
+  T *orow = out + (size_t)t * ldo + (size_t)hd * dv;
+  if (VEC) {                                          // four channels to a lane: widths in multiples of 4, rows on 16 bytes
+    float4 v[2];                                      // heads of up to 256 channels
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int i = (lane + 32 * r) * 4;
+      v[r] = i < dv ? ld4(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      ss = fmaf(v[r].x, v[r].x, ss);
+      ss = fmaf(v[r].y, v[r].y, ss);
+      ss = fmaf(v[r].z, v[r].z, ss);
+      ss = fmaf(v[r].w, v[r].w, ss);
+    }
+    float inv = 1.f;
+    if (eps >= 0.f) inv = 1.f / sqrtf(warp_sum(ss) / (float)dv + eps);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int i = (lane + 32 * r) * 4;
+      if (i >= dv) continue;
+      float4 y = make_float4(v[r].x * inv, v[r].y * inv, v[r].z * inv, v[r].w * inv);
+      if (wr) {
+        const float4 w4 = ld4(wr + i);
+        y = make_float4(y.x * w4.x, y.y * w4.y, y.z * w4.z, y.w * w4.w);
+      }
+      if (gr) {
+        const float4 g4 = ld4(gr + i);
+        y = make_float4(y.x / (1.f + expf(-g4.x)), y.y / (1.f + expf(-g4.y)), y.z / (1.f + expf(-g4.z)), y.w / (1.f + expf(-g4.w)));
+      }
+      st4(orow + i, y);
+    }
+    return;
+  }
   float inv = 1.f;
   if (eps >= 0.f) {
     float ss = 0.f;
@@ -380,9 +482,9 @@ head_norm_gate_kernel(const float *__restrict__ x, long long ldx, const float *_
   }
   for (int i = lane; i < dv; i += 32) {
     float v = xr[i] * inv;
-    if (weight) v *= weight[(size_t)hd * dv + i];
-    if (gate) v *= 1.f / (1.f + expf(-gate[(size_t)t * gate_stride + (size_t)hd * dv + i]));
-    out[(size_t)t * ldo + (size_t)hd * dv + i] = from_float<T>(v);
+    if (wr) v *= wr[i];
+    if (gr) v *= 1.f / (1.f + expf(-gr[i]));
+    orow[i] = from_float<T>(v);
   }
 }
 
@@ -393,13 +495,17 @@ LLM_EXPORT int llm_head_norm_gate(const float *x, long long ldx, const float *we
   LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && dv > 0 && x && out, "head_norm_gate: bad arguments");
   const long long items = (long long)n_tokens * n_heads;
   const dim3 grid((unsigned)((items + 3) / 4));
-  if (out_dtype == LLM_F32)
-    llm_launch(head_norm_gate_kernel<float>, grid, dim3(128), 0, stream, x, ldx, weight, gate, gate_stride, eps, n_tokens, n_heads, dv,
-               (float *)out, ldo);
-  else if (out_dtype == LLM_BF16)
-    llm_launch(head_norm_gate_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, x, ldx, weight, gate, gate_stride, eps, n_tokens,
-               n_heads, dv, (__nv_bfloat16 *)out, ldo);
+  const bool vec = dv % 4 == 0 && dv <= 256 && ldx % 4 == 0 && ldo % 4 == 0 && gate_stride % 4 == 0 && (uintptr_t)x % 16 == 0 &&
+                   (uintptr_t)weight % 16 == 0 && (uintptr_t)gate % 16 == 0 && (uintptr_t)out % 16 == 0;
+#define HNG_GO(T, VEC)                                                                                                  \
+  llm_launch(head_norm_gate_kernel<T, VEC>, grid, dim3(128), 0, stream, x, ldx, weight, gate, gate_stride, eps, n_tokens, n_heads, dv, \
+             (T *)out, ldo)
+  if (out_dtype == LLM_F32 && vec) HNG_GO(float, true);
+  else if (out_dtype == LLM_F32) HNG_GO(float, false);
+  else if (out_dtype == LLM_BF16 && vec) HNG_GO(__nv_bfloat16, true);
+  else if (out_dtype == LLM_BF16) HNG_GO(__nv_bfloat16, false);
   else LLM_FAIL("head_norm_gate: unknown dtype %d", out_dtype);
+#undef HNG_GO
   LLM_CHECK_LAUNCH("head_norm_gate");
   return LLM_OK;
 }

@@ -380,7 +380,7 @@ LLM_EXPORT int llm_qk_place(int in_dtype, int dtype, const void *qkv, long long 
 // is divided by its root mean square over dv, sqrt(mean(v^2) + v_eps), when v_eps >= 0 (no
 // weight), and is cached so.  q goes to q_out, k and v to the cache.  A CTA a token; a warp takes
 // a value head at a time (sum in lane order, then the shuffle tree).
-template <typename TI, typename T>
+template <typename TI, typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 kv_place_kernel(const TI *__restrict__ qkv, long long row_stride, T *__restrict__ q_out, long long q_stride, int n_heads,
                 int n_kv, int d, int dv, const float *__restrict__ bias, float v_eps, const int *__restrict__ tok_seq,
@@ -391,20 +391,54 @@ kv_place_kernel(const TI *__restrict__ qkv, long long row_stride, T *__restrict_
   const int t = blockIdx.x;
   const TI *row = qkv + (size_t)t * row_stride;
   const int qw = n_heads * d, kw = n_kv * d;
-  for (int c = threadIdx.x; c < qw; c += 256)
-    q_out[(size_t)t * q_stride + c] = from_float<T>(to_float(row[c]) + (bias ? bias[c] : 0.f));
+  auto add4 = [](float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); };
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (VEC) {
+    for (int c = threadIdx.x * 4; c < qw; c += 1024) st4(q_out + (size_t)t * q_stride + c, add4(ld4(row + c), bias ? ld4(bias + c) : zero4));
+  } else {
+    for (int c = threadIdx.x; c < qw; c += 256)
+      q_out[(size_t)t * q_stride + c] = from_float<T>(to_float(row[c]) + (bias ? bias[c] : 0.f));
+  }
   if (!write_cache) return;
   const int pos = tok_pos[t];
   const int page = page_table[(size_t)tok_seq[t] * pt_stride + pos / page_size];
   const size_t cache_row = (size_t)page * n_kv * page_size + (pos % page_size);
-  for (int c = threadIdx.x; c < kw; c += 256) {
-    const int kvh = c / d, ch = c - kvh * d;
-    kcache[(cache_row + (size_t)kvh * page_size) * d + ch] = from_float<T>(to_float(row[qw + c]) + (bias ? bias[qw + c] : 0.f));
+  if (VEC) {
+    for (int c = threadIdx.x * 4; c < kw; c += 1024) {
+      const int kvh = c / d, ch = c - kvh * d;
+      st4(kcache + (cache_row + (size_t)kvh * page_size) * d + ch, add4(ld4(row + qw + c), bias ? ld4(bias + qw + c) : zero4));
+    }
+  } else {
+    for (int c = threadIdx.x; c < kw; c += 256) {
+      const int kvh = c / d, ch = c - kvh * d;
+      kcache[(cache_row + (size_t)kvh * page_size) * d + ch] = from_float<T>(to_float(row[qw + c]) + (bias ? bias[qw + c] : 0.f));
+    }
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int kvh = warp; kvh < n_kv; kvh += 8) {
     const TI *v = row + qw + kw + (size_t)kvh * dv;
     const float *vb = bias ? bias + qw + kw + (size_t)kvh * dv : nullptr;
+    T *dst = vcache + (cache_row + (size_t)kvh * page_size) * dv;
+    if (VEC) {                                        // four channels to a lane, heads of up to 256 channels
+      float4 x[2];
+      float ss = 0.f;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int i = (lane + 32 * r) * 4;
+        x[r] = i < dv ? add4(ld4(v + i), vb ? ld4(vb + i) : zero4) : zero4;
+        ss = fmaf(x[r].x, x[r].x, ss);
+        ss = fmaf(x[r].y, x[r].y, ss);
+        ss = fmaf(x[r].z, x[r].z, ss);
+        ss = fmaf(x[r].w, x[r].w, ss);
+      }
+      const float inv = v_eps >= 0.f ? 1.f / sqrtf(warp_sum(ss) / (float)dv + v_eps) : 1.f;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int i = (lane + 32 * r) * 4;
+        if (i < dv) st4(dst + i, make_float4(x[r].x * inv, x[r].y * inv, x[r].z * inv, x[r].w * inv));
+      }
+      continue;
+    }
     float inv = 1.f;
     if (v_eps >= 0.f) {
       float ss = 0.f;
@@ -415,7 +449,6 @@ kv_place_kernel(const TI *__restrict__ qkv, long long row_stride, T *__restrict_
       ss = warp_sum(ss);
       inv = 1.f / sqrtf(ss / (float)dv + v_eps);
     }
-    T *dst = vcache + (cache_row + (size_t)kvh * page_size) * dv;
     for (int i = lane; i < dv; i += 32) dst[i] = from_float<T>((to_float(v[i]) + (vb ? vb[i] : 0.f)) * inv);
   }
 }
@@ -427,13 +460,21 @@ LLM_EXPORT int llm_kv_place(int in_dtype, int dtype, const void *qkv, long long 
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && d > 0 && dv > 0, "kv_place: bad sizes");
   LLM_REQUIRE(row_stride >= (long long)n_heads * d + (long long)n_kv * (d + dv), "kv_place: the stacked rows are too short");
+  // four channels to a thread where widths are multiples of 4 and rows start on 16 bytes
+  const bool vec = d % 4 == 0 && dv % 4 == 0 && dv <= 256 && row_stride % 4 == 0 && q_stride % 4 == 0 && (uintptr_t)qkv % 16 == 0 &&
+                   (uintptr_t)q_out % 16 == 0 && (uintptr_t)bias % 16 == 0 && (uintptr_t)kcache % 16 == 0 && (uintptr_t)vcache % 16 == 0;
 #define KV_PLACE(TI, T)                                                                                                  \
-  llm_launch(kv_place_kernel<TI, T>, dim3(n_tokens), dim3(256), 0, stream, (const TI *)qkv, row_stride, (T *)q_out, q_stride, \
+  if (vec)                                                                                                               \
+    llm_launch(kv_place_kernel<TI, T, true>, dim3(n_tokens), dim3(256), 0, stream, (const TI *)qkv, row_stride, (T *)q_out, q_stride, \
+               n_heads, n_kv, d, dv, bias, v_eps, tok_seq, tok_pos, page_table, pt_stride, (T *)kcache, (T *)vcache, page_size, \
+               write_cache);                                                                                             \
+  else                                                                                                                   \
+    llm_launch(kv_place_kernel<TI, T, false>, dim3(n_tokens), dim3(256), 0, stream, (const TI *)qkv, row_stride, (T *)q_out, q_stride, \
              n_heads, n_kv, d, dv, bias, v_eps, tok_seq, tok_pos, page_table, pt_stride, (T *)kcache, (T *)vcache, page_size, \
              write_cache)
-  if (in_dtype == LLM_F32 && dtype == LLM_F32) KV_PLACE(float, float);
-  else if (in_dtype == LLM_F32 && dtype == LLM_BF16) KV_PLACE(float, __nv_bfloat16);
-  else if (in_dtype == LLM_BF16 && dtype == LLM_BF16) KV_PLACE(__nv_bfloat16, __nv_bfloat16);
+  if (in_dtype == LLM_F32 && dtype == LLM_F32) { KV_PLACE(float, float); }
+  else if (in_dtype == LLM_F32 && dtype == LLM_BF16) { KV_PLACE(float, __nv_bfloat16); }
+  else if (in_dtype == LLM_BF16 && dtype == LLM_BF16) { KV_PLACE(__nv_bfloat16, __nv_bfloat16); }
   else LLM_FAIL("kv_place: unsupported dtypes in %d out %d", in_dtype, dtype);
 #undef KV_PLACE
   LLM_CHECK_LAUNCH("kv_place");
