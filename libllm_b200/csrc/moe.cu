@@ -369,9 +369,35 @@ __global__ void activation_kernel(const TI *__restrict__ in, T *__restrict__ out
     out[i] = from_float<T>(activate(to_float(in[i]), act));
 }
 
+// Four values to a thread (counts that are multiples of 4, 16-byte aligned).
+template <typename TI, typename T>
+__global__ void activation_vec_kernel(const TI *__restrict__ in, T *__restrict__ out, size_t n4, int act) {
+  grid_dependents_launch();
+  grid_dependency_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    const float4 v = ld4(in + 4 * i);
+    st4(out + 4 * i, make_float4(activate(v.x, act), activate(v.y, act), activate(v.z, act), activate(v.w, act)));
+  }
+}
+
 LLM_EXPORT int llm_activation(int in_dtype, int dtype, const void *in, void *out, long long n, int act, cudaStream_t stream) {
   if (n == 0) return LLM_OK;
   LLM_REQUIRE(n > 0 && act >= 0 && act <= 3, "activation: bad arguments");
+  if (n % 4 == 0 && (uintptr_t)in % 16 == 0 && (uintptr_t)out % 16 == 0 && (in_dtype == LLM_F32 || dtype == LLM_BF16)) {
+    const size_t n4 = (size_t)n / 4;
+    size_t blocks4 = (n4 + 255) / 256;
+    if (blocks4 > (size_t)sm_count() * 32) blocks4 = (size_t)sm_count() * 32;
+    if (in_dtype == LLM_F32 && dtype == LLM_F32)
+      llm_launch(activation_vec_kernel<float, float>, dim3((unsigned)blocks4), dim3(256), 0, stream, (const float *)in, (float *)out, n4, act);
+    else if (in_dtype == LLM_F32 && dtype == LLM_BF16)
+      llm_launch(activation_vec_kernel<float, __nv_bfloat16>, dim3((unsigned)blocks4), dim3(256), 0, stream, (const float *)in,
+                 (__nv_bfloat16 *)out, n4, act);
+    else
+      llm_launch(activation_vec_kernel<__nv_bfloat16, __nv_bfloat16>, dim3((unsigned)blocks4), dim3(256), 0, stream,
+                 (const __nv_bfloat16 *)in, (__nv_bfloat16 *)out, n4, act);
+    LLM_CHECK_LAUNCH("activation");
+    return LLM_OK;
+  }
   size_t blocks = ((size_t)n + 255) / 256;
   if (blocks > (size_t)sm_count() * 32) blocks = (size_t)sm_count() * 32;
   if (in_dtype == LLM_F32 && dtype == LLM_F32)
