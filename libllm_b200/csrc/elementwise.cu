@@ -459,6 +459,155 @@ LLM_EXPORT int llm_add_layernorm(float *resid, const void *delta, int delta_dtyp
   LLM_FAIL("add_layernorm: unknown dtypes %d, %d", delta_dtype, out_dtype);
 }
 
+// Layer norm of a step of single tokens followed by the convolution over time that the mixer's input goes
+// through (parts/builtin.cc: prenorm block, mixer_conv): row i is sequence i's one token, the taps - 1 rows before
+// it are the sequence's state[slot][0 .. taps - 2] (in out's type), which moves on by one row.  The normalised row
+// is rounded to out's type before the convolution reads it, as it is where the two are separate kernels, so that a
+// token's result is the same whether it came with a prompt or alone.  A thread reads and writes the state of its
+// own channels only.
+template <typename TD, typename TO, int THREADS, int VPT, int MAXP>
+__global__ void __launch_bounds__(THREADS)
+add_layernorm_conv_kernel(float *__restrict__ resid, const TD *__restrict__ delta, int n_parts, size_t part_stride,
+                          const float *__restrict__ weight, const float *__restrict__ bias, float eps, TO *__restrict__ out,
+                          int hidden, const float *__restrict__ conv_w, TO *__restrict__ state, const int *__restrict__ seq_slot,
+                          int taps) {
+  constexpr int MAX_KEEP = 7;            // taps - 1 of the longest convolution
+  __shared__ float scratch[THREADS / 32 + 1];
+  grid_dependents_launch();
+  const int i = blockIdx.x;
+  const int n4 = hidden / 4, keep = taps - 1;
+  float4 v[VPT], w[VPT], b[VPT], d[VPT][MAXP];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {        // the norm's weight and bias do not depend on the kernel before
+    const int c4 = threadIdx.x + j * THREADS;
+    if (c4 < n4) {
+      w[j] = ld4(weight + 4 * c4);
+      b[j] = bias ? ld4(bias + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  grid_dependency_wait();
+  float *x = resid + (size_t)i * hidden;
+  TO *st = state + (size_t)seq_slot[i] * keep * hidden;
+  float4 old[VPT][MAX_KEEP];             // the sequence's earlier rows: on their way while the norm is taken
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int c4 = threadIdx.x + j * THREADS;
+    if (c4 < n4) {
+      v[j] = ld4(x + 4 * c4);
+#pragma unroll
+      for (int p = 0; p < MAXP; ++p)
+        if (p < n_parts) d[j][p] = ld4(delta + p * part_stride + (size_t)i * hidden + 4 * c4);
+#pragma unroll
+      for (int t = 0; t < MAX_KEEP; ++t)
+        if (t < keep) old[j][t] = ld4(st + (size_t)t * hidden + 4 * c4);
+    }
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int c4 = threadIdx.x + j * THREADS;
+    if (c4 < n4) {
+#pragma unroll
+      for (int p = 0; p < MAXP; ++p)
+        if (p < n_parts) {
+          v[j].x += d[j][p].x;
+          v[j].y += d[j][p].y;
+          v[j].z += d[j][p].z;
+          v[j].w += d[j][p].w;
+        }
+      if (n_parts > 0) st4(x + 4 * c4, v[j]);
+      sum += v[j].x;
+      sum += v[j].y;
+      sum += v[j].z;
+      sum += v[j].w;
+    }
+  }
+  const float mean = block_sum<THREADS>(sum, scratch) / (float)hidden;
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int c4 = threadIdx.x + j * THREADS;
+    if (c4 < n4) {
+      v[j] = make_float4(v[j].x - mean, v[j].y - mean, v[j].z - mean, v[j].w - mean);
+      ss = fmaf(v[j].x, v[j].x, ss);
+      ss = fmaf(v[j].y, v[j].y, ss);
+      ss = fmaf(v[j].z, v[j].z, ss);
+      ss = fmaf(v[j].w, v[j].w, ss);
+    }
+  }
+  const float var = block_sum<THREADS>(ss, scratch) / (float)hidden;
+  const float inv = 1.f / sqrtf(var + eps);
+  TO *o = out + (size_t)i * hidden;
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    const int c4 = threadIdx.x + j * THREADS;
+    if (c4 >= n4) continue;
+    float h[4] = {v[j].x * inv * w[j].x + b[j].x, v[j].y * inv * w[j].y + b[j].y, v[j].z * inv * w[j].z + b[j].z,
+                  v[j].w * inv * w[j].w + b[j].w};
+    float res[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      h[e] = to_float(from_float<TO>(h[e]));      // the convolution reads the row as it is stored
+      const float *cw = conv_w + (size_t)(4 * c4 + e) * taps;
+      // the same order of operations as the convolution's own kernel: taps in order, then the token itself
+      float s = 0.f;
+#pragma unroll
+      for (int t = 0; t < MAX_KEEP; ++t)
+        if (t < keep) s = fmaf(cw[t], e == 0 ? old[j][t].x : e == 1 ? old[j][t].y : e == 2 ? old[j][t].z : old[j][t].w, s);
+      s = fmaf(cw[keep], h[e], s);
+      res[e] = h[e] + s;
+    }
+#pragma unroll
+    for (int t = 1; t < MAX_KEEP; ++t)
+      if (t < keep) st4(st + (size_t)(t - 1) * hidden + 4 * c4, old[j][t]);
+    st4(st + (size_t)(keep - 1) * hidden + 4 * c4, make_float4(h[0], h[1], h[2], h[3]));
+    st4(o + 4 * c4, make_float4(res[0], res[1], res[2], res[3]));
+  }
+}
+
+// 1 if the fused kernel takes rows of this width with this many parts pending (else: the norm, then the convolution).
+LLM_EXPORT int llm_add_layernorm_conv_supports(int hidden, int n_parts, int taps) {
+  return hidden % 4 == 0 && hidden <= 8192 && n_parts <= 8 && taps >= 2 && taps <= 8;
+}
+
+LLM_EXPORT int llm_add_layernorm_conv(float *resid, const void *delta, int delta_dtype, int n_parts, long long part_stride,
+                                      const float *weight, const float *bias, float eps, void *out, int out_dtype, int n_rows,
+                                      int hidden, const float *conv_w, void *state, const int *seq_slot, int taps,
+                                      cudaStream_t stream) {
+  if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && hidden > 0 && n_parts >= 0 && out && weight && conv_w && state && seq_slot, "add_layernorm_conv: bad arguments");
+  if (!delta) n_parts = 0;
+  LLM_REQUIRE(llm_add_layernorm_conv_supports(hidden, n_parts, taps), "add_layernorm_conv: rows of %d values with %d parts and %d taps are not taken",
+              hidden, n_parts, taps);
+  LLM_REQUIRE((uintptr_t)resid % 16 == 0 && (uintptr_t)delta % 16 == 0 && (uintptr_t)weight % 16 == 0 && (uintptr_t)bias % 16 == 0 &&
+                  (uintptr_t)out % 16 == 0 && (uintptr_t)state % 16 == 0 && part_stride % 4 == 0,
+              "add_layernorm_conv: rows must be 16-byte aligned");
+#define ADDLNC_GO(TD, TO, T_, V_, MAXP)                                                                                 \
+  llm_launch(add_layernorm_conv_kernel<TD, TO, T_, V_, MAXP>, n_rows, T_, 0, stream, resid, (const TD *)delta, n_parts, (size_t)part_stride, \
+             weight, bias, eps, (TO *)out, hidden, conv_w, (TO *)state, seq_slot, taps)
+#define ADDLNC_SIZE(TD, TO, MAXP)                                \
+  do {                                                           \
+    if (hidden <= 512) ADDLNC_GO(TD, TO, 128, 1, MAXP);          \
+    else if (hidden <= 2048) ADDLNC_GO(TD, TO, 512, 1, MAXP);    \
+    else if (hidden <= 4096) ADDLNC_GO(TD, TO, 1024, 1, MAXP);   \
+    else ADDLNC_GO(TD, TO, 1024, 2, MAXP);                       \
+  } while (0)
+#define ADDLNC_PARTS(TD, TO)                  \
+  do {                                        \
+    if (n_parts <= 1) ADDLNC_SIZE(TD, TO, 1); \
+    else if (n_parts <= 4) ADDLNC_SIZE(TD, TO, 4); \
+    else ADDLNC_SIZE(TD, TO, 8);              \
+  } while (0)
+  if (delta_dtype == LLM_F32 && out_dtype == LLM_F32) ADDLNC_PARTS(float, float);
+  else if (delta_dtype == LLM_F32 && out_dtype == LLM_BF16) ADDLNC_PARTS(float, __nv_bfloat16);
+  else LLM_FAIL("add_layernorm_conv: unsupported dtypes %d, %d", delta_dtype, out_dtype);
+#undef ADDLNC_PARTS
+#undef ADDLNC_SIZE
+#undef ADDLNC_GO
+  LLM_CHECK_LAUNCH("add_layernorm_conv");
+  return LLM_OK;
+}
+
 // ---------------------------------------------------------------- rows of the stream picked out
 // out[i] = resid[rows[i]] + sum_p delta[p][rows[i]] (32-bit, parts in index order): the residual
 // stream of the rows that anything still reads, when the others are done with.

@@ -174,6 +174,15 @@ void add_rmsnorm(float *resid, const Act *delta, const float *weight, float eps,
            has ? delta->parts : 0, has ? (long long)delta->part_stride : 0, weight, eps, out, code(out_dtype), rows, n_rows,
            hidden, s);
 }
+LLM_KERNEL("elementwise", llm_add_layernorm_conv, float *, const void *, int, int, long long, const float *, const float *, float, void *,
+           int, int, int, const float *, void *, const int *, int, cudaStream_t)
+void add_layernorm_conv(float *resid, const Act *delta, const float *weight, const float *bias, float eps, void *out, DType out_dtype,
+                        int n_rows, int hidden, const float *conv_w, void *state, const int *seq_slot, int taps, cudaStream_t s) {
+  const bool has = delta && delta->data;
+  LLM_CALL("elementwise", llm_add_layernorm_conv, resid, has ? delta->data : nullptr, has ? code(delta->dtype) : 0,
+           has ? delta->parts : 0, has ? (long long)delta->part_stride : 0, weight, bias, eps, out, code(out_dtype), n_rows, hidden,
+           conv_w, state, seq_slot, taps, s);
+}
 void gather_rows_add(const float *resid, const Act *delta, const int *rows, int n_rows, float *out, int hidden, cudaStream_t s) {
   const bool has = delta && delta->data;
   LLM_CALL("elementwise", llm_gather_rows_add, resid, has ? delta->data : nullptr, has ? code(delta->dtype) : 0, has ? delta->parts : 0,
@@ -301,7 +310,7 @@ LLM_KERNEL("attention_generic", llm_attention_generic, int, const void *, long l
            cudaStream_t)
 LLM_KERNEL("attention_decode", llm_attention_decode_sink, const void *, long long, void *, long long, const void *, const void *,
            const int *, const int *, int, int, int, int, int, int, int, int, int, int, int, float, float *, float *, const float *,
-           long long, cudaStream_t)
+           long long, int, cudaStream_t)
 LLM_KERNEL("attention_decode_tc", llm_attention_decode_tc, const float *, long long, int, long long, const float *, int, int,
            const int *, const int *, int, void *, void *, int, int, int, int, int, int, int, int, int, int, int, float, float *,
            float *, int *, void *, long long, cudaStream_t)
@@ -329,11 +338,11 @@ bool attention_decode_supported(int d, int group) {
 void attention_decode(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                       int pt_stride, int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window,
                       int block, float scale, float *ws_o, float *ws_ml, const float *gate, long long gate_stride,
-                      cudaStream_t s, int sink) {
+                      cudaStream_t s, int sink, bool gate_per_channel) {
   const int B = (int)q.rows;
   LLM_CALL("attention_decode", llm_attention_decode_sink, q.data, (long long)(B > 1 ? q.ld : q.cols), out.data,
            (long long)(B > 1 ? out.ld : out.cols), kc, vc, tok_pos, page_table, pt_stride, B, n_heads, n_kv, d, page_size, chunk,
-           n_splits, window, block, sink, scale, ws_o, ws_ml, gate, gate_stride, s);
+           n_splits, window, block, sink, scale, ws_o, ws_ml, gate, gate_stride, gate_per_channel ? 1 : 0, s);
 }
 bool attention_decode_tc_supported(int d, int page_size, int group) {
   static auto f = resolve<int (*)(int, int, int)>("attention_decode_tc", "llm_attention_decode_tc_supports");
@@ -454,6 +463,20 @@ void delta_rule(const Act &proj, int off_r, int off_k, int off_v, int off_a, int
   LLM_CALL("recurrent", llm_delta_rule, (const float *)proj.data, (long long)proj.ld, off_r, off_k, off_v, off_a, off_x1, rank, w2, w0,
            a_bias, decay_scale, key_eps, prep, state, (float *)out.data, (long long)out.ld, seq_start, seq_slot, (int)proj.rows,
            n_seqs, n_heads, d, s);
+}
+LLM_KERNEL("recurrent", llm_delta_step, const float *, long long, int, int, int, int, int, int, int, const float *, const float *,
+           const float *, float, float, const float *, float, float *, void *, int, long long, const int *, int, int, int, cudaStream_t)
+bool delta_step_supported(int d) {
+  static auto f = resolve<int (*)(int)>("recurrent", "llm_delta_step_supports");
+  return f(d) != 0;
+}
+void delta_step(const Act &proj, int off_r, int off_k, int off_v, int off_g, int off_a, int off_x1, int rank, const float *w2,
+                const float *w0, const float *a_bias, float decay_scale, float key_eps, const float *norm_w, float eps, float *state,
+                const Act &out, const int *seq_slot, int n_heads, int d, cudaStream_t s) {
+  if (proj.dtype != DType::F32) LLM_THROW(InvalidArg, "delta_step: projections are 32-bit");
+  LLM_CALL("recurrent", llm_delta_step, (const float *)proj.data, (long long)proj.ld, off_r, off_k, off_v, off_g, off_a, off_x1, rank,
+           w2, w0, a_bias, decay_scale, key_eps, norm_w, eps, state, out.data, code(out.dtype), (long long)out.ld, seq_slot,
+           (int)proj.rows, n_heads, d, s);
 }
 void head_norm_gate(const Act &x, const float *weight, const float *gate, long long gate_stride, float eps, int n_heads, int dv,
                     const Act &out, cudaStream_t s) {

@@ -35,6 +35,10 @@ void add_rmsnorm(float *resid, const Act *delta, const float *weight, float eps,
 // The same pass with a layer norm: (v - mean) / sqrt(var + eps) * weight + bias (bias may be null).
 void add_layernorm(float *resid, const Act *delta, const float *weight, const float *bias, float eps, void *out, DType out_dtype,
                    const int *rows, int n_rows, int hidden, cudaStream_t s);
+// A step of single tokens: the layer norm of every row, then out = h + conv(h) over time with the taps - 1 rows of
+// state[seq_slot[row]] (in out's type), which move on by one.
+void add_layernorm_conv(float *resid, const Act *delta, const float *weight, const float *bias, float eps, void *out, DType out_dtype,
+                        int n_rows, int hidden, const float *conv_w, void *state, const int *seq_slot, int taps, cudaStream_t s);
 // out[i] = resid[rows[i]] + delta's parts at that row (32-bit)
 void gather_rows_add(const float *resid, const Act *delta, const int *rows, int n_rows, float *out, int hidden, cudaStream_t s);
 void swiglu(const Act &gu, void *out, DType out_dtype, cudaStream_t s);
@@ -103,7 +107,7 @@ bool attention_decode_supported(int d, int group);
 void attention_decode(const Act &q, const Act &out, const void *kc, const void *vc, const int *tok_pos, const int *page_table,
                       int pt_stride, int n_heads, int n_kv, int d, int page_size, int chunk, int n_splits, int window,
                       int block, float scale, float *ws_o, float *ws_ml, const float *gate, long long gate_stride,
-                      cudaStream_t s, int sink = 0);
+                      cudaStream_t s, int sink = 0, bool gate_per_channel = false);
 bool attention_decode_tc_supported(int d, int page_size, int group);
 int attention_decode_tc_ctas_per_sm(int d);
 void attention_decode_tc(const Act &qkv, const float *table, int table_rows, int rot_dim, const int *tok_pos,
@@ -153,6 +157,12 @@ void causal_conv(const Act &h, const Act &out, const float *weight, void *state,
 void delta_rule(const Act &proj, int off_r, int off_k, int off_v, int off_a, int off_x1, int rank, const float *w2, const float *w0,
                 const float *a_bias, float decay_scale, float key_eps, float *prep, float *state, const Act &out,
                 const int *seq_start, const int *seq_slot, int n_seqs, int n_heads, int d, cudaStream_t s);
+// A step of single tokens (row b = sequence b): the same, with the norm over each head, its weight and the gate
+// (logits at off_g of the rows) behind it, in one launch; out [sequences, heads * d] in the engine's type.
+bool delta_step_supported(int d);
+void delta_step(const Act &proj, int off_r, int off_k, int off_v, int off_g, int off_a, int off_x1, int rank, const float *w2,
+                const float *w0, const float *a_bias, float decay_scale, float key_eps, const float *norm_w, float eps, float *state,
+                const Act &out, const int *seq_slot, int n_heads, int d, cudaStream_t s);
 // out[t, h, :] = x / rms(x over the head; eps < 0: no norm) * weight (null: none) * sigmoid(gate) (null: none)
 void head_norm_gate(const Act &x, const float *weight, const float *gate, long long gate_stride, float eps, int n_heads, int dv,
                     const Act &out, cudaStream_t s);

@@ -388,7 +388,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, v
                      tok_pos: torch.Tensor, page_table: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
                      page_size: int, chunk: int, n_splits: int, window: Optional[int], scale: float,
                      ws_o: Optional[torch.Tensor], ws_ml: Optional[torch.Tensor], block: Optional[int] = None,
-                     gate: Optional[torch.Tensor] = None, sink: int = 0) -> torch.Tensor:
+                     gate: Optional[torch.Tensor] = None, sink: int = 0, gate_per_channel: bool = False) -> torch.Tensor:
     """One query token per sequence over the paged cache, keys split into ``n_splits``
     runs of ``chunk``; ``ws_o``/``ws_ml`` are the scratch the splits are joined through."""
     _on_gpu(q, out, kcache, vcache, tok_pos, page_table, ws_o, ws_ml)
@@ -400,11 +400,11 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, kcache: torch.Tensor, v
         assert ws_ml.dtype == torch.float32 and ws_ml.numel() >= B * n_heads * n_splits * 2
     _call("attention_decode", "llm_attention_decode_sink",
           [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p],
+           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p],
           _ptr(q), q.stride(0) if B > 1 else q.shape[1], _ptr(out), out.stride(0) if B > 1 else out.shape[1],
           _ptr(kcache), _ptr(vcache), _ptr(tok_pos), _ptr(page_table), page_table.stride(0), B, n_heads, n_kv,
           head_dim, page_size, chunk, n_splits, int(window or 0), int(block or 0), int(sink or 0), float(scale), _ptr(ws_o), _ptr(ws_ml), _ptr(gate),
-          gate.stride(0) if gate is not None else 0, _stream())
+          gate.stride(0) if gate is not None else 0, 1 if gate_per_channel else 0, _stream())
     return out
 
 

@@ -283,6 +283,46 @@ __device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async
 template <int N>
 __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// One token of one column: this thread's share S[ROWS] of the column, the token's vectors w, b, u, k, r (each
+// VLEN floats on; `vecs` points at this thread's share of w, 16-byte aligned), the column's value v.  Returns the
+// column's read-out S^T r, summed over the LANES lanes of the column.  Sums run over four partial sums in a
+// fixed order, then the lanes' shuffle tree: the same wherever a token is computed.
+template <int ROWS, int LANES>
+__device__ __forceinline__ float delta_token(float (&S)[ROWS], const float *vecs, int VLEN, float v) {
+  const float4 *w4 = reinterpret_cast<const float4 *>(vecs), *b4 = reinterpret_cast<const float4 *>(vecs + VLEN);
+  const float4 *u4 = reinterpret_cast<const float4 *>(vecs + 2 * VLEN), *k4 = reinterpret_cast<const float4 *>(vecs + 3 * VLEN);
+  const float4 *r4 = reinterpret_cast<const float4 *>(vecs + 4 * VLEN);
+  float p4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < ROWS / 4; ++i) {
+    const float4 uu = u4[i];
+    p4[0] = fmaf(uu.x, S[4 * i], p4[0]);
+    p4[1] = fmaf(uu.y, S[4 * i + 1], p4[1]);
+    p4[2] = fmaf(uu.z, S[4 * i + 2], p4[2]);
+    p4[3] = fmaf(uu.w, S[4 * i + 3], p4[3]);
+  }
+  float us = (p4[0] + p4[1]) + (p4[2] + p4[3]);
+#pragma unroll
+  for (int o = 1; o < LANES; o <<= 1) us += __shfl_xor_sync(0xffffffffu, us, o);
+  float a4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < ROWS / 4; ++i) {
+    const float4 ww = w4[i], bq = b4[i], kk = k4[i], rr = r4[i];
+    S[4 * i] = fmaf(ww.x, S[4 * i], fmaf(kk.x, v, -bq.x * us));
+    S[4 * i + 1] = fmaf(ww.y, S[4 * i + 1], fmaf(kk.y, v, -bq.y * us));
+    S[4 * i + 2] = fmaf(ww.z, S[4 * i + 2], fmaf(kk.z, v, -bq.z * us));
+    S[4 * i + 3] = fmaf(ww.w, S[4 * i + 3], fmaf(kk.w, v, -bq.w * us));
+    a4[0] = fmaf(S[4 * i], rr.x, a4[0]);
+    a4[1] = fmaf(S[4 * i + 1], rr.y, a4[1]);
+    a4[2] = fmaf(S[4 * i + 2], rr.z, a4[2]);
+    a4[3] = fmaf(S[4 * i + 3], rr.w, a4[3]);
+  }
+  float acc = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+#pragma unroll
+  for (int o = 1; o < LANES; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  return acc;
+}
+
 template <int DMAX, int LANES, bool VEC>
 __global__ void __launch_bounds__(DR_THREADS)
 delta_rule_kernel(const float *__restrict__ proj, long long ld, int off_r, int off_k, int off_v,
@@ -345,40 +385,7 @@ delta_rule_kernel(const float *__restrict__ proj, long long ld, int off_r, int o
   };
   auto token = [&](int t) {
     const float *slot = ring[t % DR_STAGES];
-    const float *w = slot + sub * PAD, *bb = w + VLEN, *u = bb + VLEN, *k = u + VLEN, *r = k + VLEN;
-    const float v = slot[5 * VLEN + col];
-    // a lane's share of every vector starts on 16 bytes (PAD and VLEN are multiples of 4): four values to a load
-    const float4 *w4 = reinterpret_cast<const float4 *>(w), *b4 = reinterpret_cast<const float4 *>(bb);
-    const float4 *u4 = reinterpret_cast<const float4 *>(u), *k4 = reinterpret_cast<const float4 *>(k);
-    const float4 *r4 = reinterpret_cast<const float4 *>(r);
-    float p4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int i = 0; i < ROWS / 4; ++i) {
-      const float4 uu = u4[i];
-      p4[0] = fmaf(uu.x, S[4 * i], p4[0]);
-      p4[1] = fmaf(uu.y, S[4 * i + 1], p4[1]);
-      p4[2] = fmaf(uu.z, S[4 * i + 2], p4[2]);
-      p4[3] = fmaf(uu.w, S[4 * i + 3], p4[3]);
-    }
-    float us = (p4[0] + p4[1]) + (p4[2] + p4[3]);
-#pragma unroll
-    for (int o = 1; o < LANES; o <<= 1) us += __shfl_xor_sync(0xffffffffu, us, o);
-    float a4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int i = 0; i < ROWS / 4; ++i) {
-      const float4 ww = w4[i], bq = b4[i], kk = k4[i], rr = r4[i];
-      S[4 * i] = fmaf(ww.x, S[4 * i], fmaf(kk.x, v, -bq.x * us));
-      S[4 * i + 1] = fmaf(ww.y, S[4 * i + 1], fmaf(kk.y, v, -bq.y * us));
-      S[4 * i + 2] = fmaf(ww.z, S[4 * i + 2], fmaf(kk.z, v, -bq.z * us));
-      S[4 * i + 3] = fmaf(ww.w, S[4 * i + 3], fmaf(kk.w, v, -bq.w * us));
-      a4[0] = fmaf(S[4 * i], rr.x, a4[0]);
-      a4[1] = fmaf(S[4 * i + 1], rr.y, a4[1]);
-      a4[2] = fmaf(S[4 * i + 2], rr.z, a4[2]);
-      a4[3] = fmaf(S[4 * i + 3], rr.w, a4[3]);
-    }
-    float acc = (a4[0] + a4[1]) + (a4[2] + a4[3]);
-#pragma unroll
-    for (int o = 1; o < LANES; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    const float acc = delta_token<ROWS, LANES>(S, slot + sub * PAD, VLEN, slot[5 * VLEN + col]);
     if (live && sub == 0) out[(size_t)(start + t) * ldo + (size_t)hd * d + j] = acc;
   };
   // Tokens go through the ring in pairs: a group of copies is a pair, DR_STAGES / 2 - 1 pairs are in flight, and a
@@ -449,6 +456,120 @@ LLM_EXPORT int llm_delta_rule(const float *proj, long long ld, int off_r, int of
 #undef DR_GO2
 #undef DR_GO
   LLM_CHECK_LAUNCH("delta_rule");
+  return LLM_OK;
+}
+
+// ---------------------------------------------------------------- the delta rule: a step of single tokens
+// Everything between the stacked product and the output projection in one launch, a CTA per (sequence, head):
+// the token's vectors (as delta_prepare_kernel makes them), the state's step (delta_token, the scan's own
+// arithmetic, with all of the head's columns in this CTA), the norm over the head, its weight and the gate.
+template <int DMAX, int LANES, typename TO>
+__global__ void __launch_bounds__(DMAX *LANES)
+delta_step_kernel(const float *__restrict__ proj, long long ld, int off_r, int off_k, int off_v, int off_g, int off_a, int off_x1,
+                  int rank, const float *__restrict__ w2, const float *__restrict__ w0, const float *__restrict__ a_bias,
+                  float decay_scale, float key_eps, const float *__restrict__ norm_w, float eps, float *__restrict__ state,
+                  TO *__restrict__ out, long long ldo, const int *__restrict__ seq_slot, int n_heads, int d, int w2_shared) {
+  constexpr int ROWS = DMAX / LANES, PAD = ROWS + 4, VLEN = LANES * PAD, THREADS = DMAX * LANES;
+  __shared__ __align__(16) float vecs[5 * VLEN];
+  __shared__ float vals[DMAX], outs[DMAX], red[2];
+  extern __shared__ float th[];                       // tanh of the low-rank input, `rank` floats; then W2's rows of the head, [d][rank + 1]
+  grid_dependents_launch();
+  const int b = blockIdx.x, hd = blockIdx.y;
+  const int tid = threadIdx.x, sub = tid % LANES, col = tid / LANES, lane = tid & 31, warp = tid >> 5;
+  const bool live = col < d;
+  for (int i = tid; i < 5 * VLEN; i += THREADS) vecs[i] = 0.f;
+  float *w2s = th + rank;
+  if (w2_shared) {                                    // weights: on their way before the step's own data is waited for
+    const float *w2h = w2 + (size_t)hd * d * rank;
+    for (int i = tid; i < d * rank; i += THREADS) w2s[(i / rank) * (rank + 1) + i % rank] = w2h[i];
+  }
+  grid_dependency_wait();
+  const float *row = proj + (size_t)b * ld;
+  const float *k = row + off_k + (size_t)hd * d;
+  // this thread's share of its column of the state: on its way while the vectors are made
+  float S[ROWS];
+  float *sp = state + (((size_t)seq_slot[b] * n_heads + hd) * d + (live ? col : 0)) * d + sub * ROWS;
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) S[i] = (live && sub * ROWS + i < d) ? sp[i] : 0.f;
+  for (int q = tid; q < rank; q += THREADS) th[q] = tanhf(row[off_x1 + q]);
+  if (warp == 0) {                                    // the key's length: lane order, then the shuffle tree
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) ss = fmaf(k[i], k[i], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) red[0] = 1.f / sqrtf(ss + key_eps);
+  }
+  __syncthreads();
+  if (tid < d) {
+    const int i = tid, ch = hd * d + i;
+    float z = w0[ch];
+    const float *w2r = w2_shared ? w2s + i * (rank + 1) : w2 + (size_t)ch * rank;
+    for (int q = 0; q < rank; ++q) z = fmaf(w2r[q], th[q], z);
+    const float u = k[i] * red[0];
+    const float a = 1.f / (1.f + expf(-(row[off_a + ch] + a_bias[ch])));
+    const int at = (i / ROWS) * PAD + i % ROWS;
+    vecs[at] = expf(-decay_scale / (1.f + expf(-z)));
+    vecs[VLEN + at] = a * u;
+    vecs[2 * VLEN + at] = u;
+    vecs[3 * VLEN + at] = k[i];
+    vecs[4 * VLEN + at] = row[off_r + ch];
+    vals[i] = row[off_v + ch];
+  }
+  __syncthreads();
+  const float acc = delta_token<ROWS, LANES>(S, vecs + sub * PAD, VLEN, live ? vals[col] : 0.f);
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i)
+      if (sub * ROWS + i < d) sp[i] = S[i];
+    if (sub == 0) outs[col] = acc;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    float ss = 0.f;
+    for (int i = lane; i < d; i += 32) ss = fmaf(outs[i], outs[i], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) red[1] = 1.f / sqrtf(ss / (float)d + eps);
+  }
+  __syncthreads();
+  if (tid < d) {
+    const int ch = hd * d + tid;
+    const float g = row[off_g + ch];
+    out[(size_t)b * ldo + ch] = from_float<TO>(outs[tid] * red[1] * norm_w[ch] / (1.f + expf(-g)));
+  }
+}
+
+// 1 if a step of single tokens with heads of d channels has a kernel of its own.
+LLM_EXPORT int llm_delta_step_supports(int d) { return d <= 128; }
+
+LLM_EXPORT int llm_delta_step(const float *proj, long long ld, int off_r, int off_k, int off_v, int off_g, int off_a, int off_x1,
+                              int rank, const float *w2, const float *w0, const float *a_bias, float decay_scale, float key_eps,
+                              const float *norm_w, float eps, float *state, void *out, int out_dtype, long long ldo,
+                              const int *seq_slot, int n_seqs, int n_heads, int d, cudaStream_t stream) {
+  if (n_seqs == 0) return LLM_OK;
+  LLM_REQUIRE(n_seqs > 0 && n_heads > 0 && d > 0 && rank > 0 && llm_delta_step_supports(d), "delta_step: bad sizes");
+  LLM_REQUIRE(n_heads <= 65535, "delta_step: too many heads");
+  const size_t with_w2 = ((size_t)rank + (size_t)d * (rank + 1)) * sizeof(float);
+  const int w2_shared = with_w2 <= 64 * 1024;
+  const size_t smem = w2_shared ? with_w2 : (size_t)rank * sizeof(float);
+  LLM_REQUIRE(smem <= 64 * 1024, "delta_step: a decay input of rank %d is not supported", rank);
+#define DS_GO(DMAX, LANES, TO)                                                                                          \
+  do {                                                                                                                  \
+    LLM_CHECK_CUDA(llm_allow_smem(delta_step_kernel<DMAX, LANES, TO>, smem), "delta_step attribute");                   \
+    llm_launch(delta_step_kernel<DMAX, LANES, TO>, dim3(n_seqs, n_heads), dim3(DMAX * LANES), smem, stream, proj, ld, off_r, off_k, \
+               off_v, off_g, off_a, off_x1, rank, w2, w0, a_bias, decay_scale, key_eps, norm_w, eps, state, (TO *)out, ldo, seq_slot, \
+               n_heads, d, w2_shared);                                                                                  \
+  } while (0)
+#define DS_SIZES(TO)                     \
+  do {                                   \
+    if (d <= 32) DS_GO(32, 2, TO);       \
+    else if (d <= 64) DS_GO(64, 4, TO);  \
+    else DS_GO(128, 4, TO);              \
+  } while (0)
+  if (out_dtype == LLM_F32) DS_SIZES(float);
+  else if (out_dtype == LLM_BF16) DS_SIZES(__nv_bfloat16);
+  else LLM_FAIL("delta_step: unknown dtype %d", out_dtype);
+#undef DS_SIZES
+#undef DS_GO
+  LLM_CHECK_LAUNCH("delta_step");
   return LLM_OK;
 }
 

@@ -86,6 +86,19 @@ class LayerNorm : public Norm {
     if (!rows) stream.pending = Act();
     return out;
   }
+  bool forward_conv(StepContext &ctx, ResidualStream &stream, const TimeConv &conv, Act *out) override {
+    if (!ctx.decode_only || conv.taps < 2 || conv.taps > 8 || !conv.state || stream.rows != ctx.n_seqs) return false;
+    // the fused kernel keeps the row in registers, four values to a load
+    const Act &pend = stream.pending;
+    if (size_ % 4 || size_ > 8192 || (pend.data && (pend.dtype != DType::F32 || pend.parts > 8 || pend.part_stride % 4))) return false;
+    *out = ctx.arena->act(ctx.dtype, stream.rows, size_);
+    flush_chain(ctx);
+    kernels::add_layernorm_conv(stream.resid, stream.pending.data ? &stream.pending : nullptr, weight_.buf.as<float>(),
+                                bias_name_.empty() ? nullptr : bias_.buf.as<float>(), (float)eps_, out->data, ctx.dtype, (int)stream.rows,
+                                (int)size_, conv.weight, conv.state, ctx.seq_slot, conv.taps, ctx.stream);
+    stream.pending = Act();
+    return true;
+  }
 
  private:
   int64_t size_;
@@ -440,9 +453,10 @@ class Attention : public Mixer {
           ws_ml = ctx.arena->alloc_n<float>((size_t)ctx.n_seqs * n_heads_ * n_splits * 2);
         }
         kernels::attention_decode(q, out, cache->k, cache->v, ctx.tok_pos, cache->page_table, cache->table_width, n_heads_, n_kv_,
-                                  d_, cache->page_size, chunk, n_splits, window_, block_, scale_, ws_o, ws_ml, gate, qkv.ld,
-                                  ctx.stream, sink_);
+                                  d_, cache->page_size, chunk, n_splits, window_, block_, scale_, ws_o, ws_ml,
+                                  channel_gate ? channel_gate : gate, qkv.ld, ctx.stream, sink_, channel_gate != nullptr);
         gate = nullptr;                 // applied
+        channel_gate = nullptr;
         done = true;
       } else if (f.prefill_attention_tc && (d_ == 64 || d_ == 128) && kernels::available("attention_prefill_tc") &&
                  kernels::attention_prefill_tc_supported(d_, cache->page_size)) {
@@ -614,7 +628,7 @@ class PreNormBlock : public Block {
       ctx.sink_rows = stream.rows;
       ctx.sink_cols = stream.hidden;
     };
-    Act h = mixer_norm_->forward(ctx, stream);
+    Act h;
     StateView mixer_state;
     if (taps_ > 0) {
       void *conv_state = nullptr;
@@ -624,12 +638,22 @@ class PreNormBlock : public Block {
           else mixer_state.push_back(t);
         }
       if (taps_ > 1 && !conv_state) LLM_THROW(InvalidArg, "prenorm block: the run has no state for its convolution");
-      flush_chain(ctx);
-      Act mixed = ctx.arena->act(ctx.dtype, h.rows, h.cols);
-      kernels::causal_conv(h, mixed, conv_.buf.as<float>(), conv_state, ctx.tok_seq, ctx.tok_pos, ctx.seq_start, ctx.seq_past,
-                           ctx.seq_slot, ctx.n_seqs, taps_, ctx.decode_only, ctx.stream);
-      h = mixed;
+      TimeConv conv;
+      conv.weight = conv_.buf.as<float>();
+      conv.state = conv_state;
+      conv.taps = taps_;
+      // a step of single tokens: the norm runs the convolution in its own launch where it can
+      if (!mixer_norm_->forward_conv(ctx, stream, conv, &h)) {
+        h = mixer_norm_->forward(ctx, stream);
+        flush_chain(ctx);
+        Act mixed = ctx.arena->act(ctx.dtype, h.rows, h.cols);
+        kernels::causal_conv(h, mixed, conv.weight, conv.state, ctx.tok_seq, ctx.tok_pos, ctx.seq_start, ctx.seq_past, ctx.seq_slot,
+                             ctx.n_seqs, taps_, ctx.decode_only, ctx.stream);
+        h = mixed;
+      }
       state = mixer_state.empty() ? nullptr : &mixer_state;
+    } else {
+      h = mixer_norm_->forward(ctx, stream);
     }
     sink(true);
     Act r = mixer_->forward(ctx, h, cache, state);

@@ -216,9 +216,23 @@ class Part {
   BuildEnv env_;
 };
 
+// A causal convolution over time on each channel whose result is added to its input (csrc/recurrent.cu):
+// weight [width, taps] 32-bit on the device, the last taps - 1 inputs of every sequence in state [slots, taps - 1, width].
+struct TimeConv {
+  const float *weight = nullptr;
+  void *state = nullptr;
+  int taps = 0;
+};
+
 class Norm : public Part {
  public:
   using Part::Part;
+  // A norm that can run the convolution behind it in the same launch for a step of single tokens does so, puts the
+  // result into *out and returns true; the stream's pending addition is applied as in forward().
+  virtual bool forward_conv(StepContext &ctx, ResidualStream &stream, const TimeConv &conv, Act *out) {
+    (void)ctx, (void)stream, (void)conv, (void)out;
+    return false;
+  }
   // Applies stream.pending (in 32-bit) first.  With `rows` only those rows are normalised and the
   // residual stream is left as it is.
   virtual Act forward(StepContext &ctx, ResidualStream &stream, const int *rows = nullptr, int n_rows = 0) = 0;

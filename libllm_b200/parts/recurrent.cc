@@ -90,9 +90,17 @@ class GeneralDelta : public Mixer {
     Act proj = linear(ctx, x, w_in_, nullptr, DType::F32);
     flush_chain(ctx);
     const int T = ctx.n_tokens;
+    const int W = (int)width_;
+    if (ctx.decode_only && T == ctx.n_seqs && kernels::delta_step_supported(d_)) {
+      // a step of single tokens: the vectors, the state's step, the norm and the gate in one launch
+      Act y = ctx.arena->act(ctx.dtype, T, width_);
+      kernels::delta_step(proj, 0, W, 2 * W, 3 * W, 4 * W, 5 * W, (int)rank_, w2_.buf.as<float>(), w0_.buf.as<float>(),
+                          a_bias_.buf.as<float>(), decay_scale_, key_eps_, norm_.buf.as<float>(), eps_, S, y, ctx.seq_slot, n_heads_, d_,
+                          ctx.stream);
+      return linear(ctx, y, w_o_, nullptr, DType::F32, true);
+    }
     float *prep = ctx.arena->alloc_n<float>((size_t)T * (size_t)width_ * 3);
     Act o = ctx.arena->act(DType::F32, T, width_);
-    const int W = (int)width_;
     kernels::delta_rule(proj, 0, W, 2 * W, 4 * W, 5 * W, (int)rank_, w2_.buf.as<float>(), w0_.buf.as<float>(), a_bias_.buf.as<float>(),
                         decay_scale_, key_eps_, prep, S, o, ctx.seq_start, ctx.seq_slot, ctx.n_seqs, n_heads_, d_, ctx.stream);
     Act y = ctx.arena->act(ctx.dtype, T, width_);
