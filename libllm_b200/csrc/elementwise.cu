@@ -409,7 +409,7 @@ static int launch_add_layernorm(float *resid, const void *delta, int n_parts, si
                                 cudaStream_t stream) {
   const bool aligned = hidden % 4 == 0 && (uintptr_t)resid % 16 == 0 && (uintptr_t)delta % 16 == 0 && (uintptr_t)weight % 16 == 0 &&
                        (uintptr_t)bias % 16 == 0 && (uintptr_t)out % 16 == 0 && part_stride % 4 == 0;
-  if (aligned && hidden <= 8192 && n_parts <= 4) {
+  if (aligned && hidden <= 8192 && n_parts <= 16) {
 #define ADDLN_GO(T_, V_, MAXP)                                                                            \
   llm_launch(add_layernorm_vec_kernel<TD, TO, T_, V_, MAXP>, n_rows, T_, 0, stream, resid, (const TD *)delta, n_parts, part_stride, \
              weight, bias, eps, (TO *)out, rows, hidden)
@@ -420,8 +420,11 @@ static int launch_add_layernorm(float *resid, const void *delta, int n_parts, si
     else if (hidden <= 4096) ADDLN_GO(1024, 1, MAXP);       \
     else ADDLN_GO(1024, 2, MAXP);                           \
   } while (0)
+    // one instantiation per bound on the parts (a prompt step has one part and thousands of rows)
     if (n_parts <= 1) ADDLN_SIZE(1);
-    else ADDLN_SIZE(4);
+    else if (n_parts <= 4) ADDLN_SIZE(4);
+    else if (n_parts <= 8) ADDLN_SIZE(8);
+    else ADDLN_SIZE(16);
 #undef ADDLN_SIZE
 #undef ADDLN_GO
     LLM_CHECK_LAUNCH("add_layernorm");
