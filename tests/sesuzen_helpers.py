@@ -50,6 +50,8 @@ def config(vocab, width, eps, taps, cap, layers, loop=None, max_positions=512):
 #     any test sequence, a loop that runs once, all experts chosen, delta heads of 128 and a rank of 24.
 # S5: five taps, delta heads of 8 and of 32, full attention without a mask, an empty loop.
 # S6: no routed layer: in bfloat16 whole sequences are judged.
+# S7: widths that are multiples of 2 only (no 16-byte rows anywhere), delta heads of 10 with a rank of 3, two key/value
+#     heads for six query heads of 18 with values of 6, six taps, a cap that binds (logits beyond it).
 CONFIGS: Dict[str, dict] = {
     "S1": config(150, 64, 1e-6, 3, 20.0,
                  [layer(delta(2, 16), dense(96)), layer(attn(4, 2, 16, 16, 24, 3, scale=0.2), moe(4, 2, 32))], loop=(0, 2, 2)),
@@ -68,9 +70,12 @@ CONFIGS: Dict[str, dict] = {
     "S6": config(180, 96, 1e-5, 4, 30.0,
                  [layer(attn(2, 1, 64, 64, 72, 4), dense(128)), layer(delta(3, 32), dense(72)),
                   layer(attn(4, 2, 32, 32, 40, 9, scale=0.15), None), layer(delta(2, 48), dense(64))], loop=(1, 3, 2)),
+    "S7": config(90, 50, 3e-6, 6, 4.0,
+                 [layer(delta(3, 10), dense(34)), layer(attn(6, 2, 18, 6, 21, 2, scale=0.25), moe(3, 2, 22)),
+                  layer(delta(1, 22), None)], loop=(0, 2, 2)),
 }
 # the rank of the decay's low-rank input where the configuration does not give it: read from the tensor
-RANKS = {"S1": 8, "S2": 5, "S3": 16, "S4": 24, "S5": 12, "S6": 7}
+RANKS = {"S1": 8, "S2": 5, "S3": 16, "S4": 24, "S5": 12, "S6": 7, "S7": 3}
 
 
 def is_routed(c: dict) -> bool:
