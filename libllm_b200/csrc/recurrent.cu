@@ -267,8 +267,10 @@ delta_prepare_kernel(const float *__restrict__ proj, long long ld, int off_k, in
 // each with d / LANES of its rows in registers, own column j for the whole step and walk the
 // sequence's tokens in order.  The tokens' vectors (w, b, u from the preparation, k and r from the
 // product's rows, the CTA's columns of v) come through a ring of 8 or 16 tokens in shared memory,
-// filled by asynchronous copies that run that many tokens ahead (what a token needs was written by the kernels just before and may come from DRAM) of the arithmetic, so that a token
-// costs its arithmetic and half a barrier, not a trip to memory.  Sums run over four partial sums in
+// filled by a third warp's asynchronous copies that run that many tokens ahead of the arithmetic (what a token
+// needs was written by the kernels just before and may come from DRAM), so that a token costs its arithmetic and a
+// share of a barrier, not a trip to memory.  (Issued by the warps of the recurrence themselves, the copies and their
+// address arithmetic cost a scan of 2,048 tokens 0.3 ms of its 0.86.)  Sums run over four partial sums in
 // a fixed order, then the lanes' shuffle tree.  state[slot][head][j][i] (a column's rows together).
 constexpr int DR_THREADS = 64;
 constexpr int DR_STAGES_MAX = 16;                   // tokens of the ring: 16 where they fit 48 KB of shared memory, else 8
@@ -302,16 +304,26 @@ __device__ __forceinline__ float delta_token(float (&S)[ROWS], const float *vecs
     p4[3] = fmaf(uu.w, S[4 * i + 3], p4[3]);
   }
   float us = (p4[0] + p4[1]) + (p4[2] + p4[3]);
+  // what does not wait for u^T S is taken while its shuffles are on their way: e = w S + k v, then S = e - b (u^T S)
+  float e[ROWS];
+#pragma unroll
+  for (int i = 0; i < ROWS / 4; ++i) {
+    const float4 ww = w4[i], kk = k4[i];
+    e[4 * i] = fmaf(ww.x, S[4 * i], kk.x * v);
+    e[4 * i + 1] = fmaf(ww.y, S[4 * i + 1], kk.y * v);
+    e[4 * i + 2] = fmaf(ww.z, S[4 * i + 2], kk.z * v);
+    e[4 * i + 3] = fmaf(ww.w, S[4 * i + 3], kk.w * v);
+  }
 #pragma unroll
   for (int o = 1; o < LANES; o <<= 1) us += __shfl_xor_sync(0xffffffffu, us, o);
   float a4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int i = 0; i < ROWS / 4; ++i) {
-    const float4 ww = w4[i], bq = b4[i], kk = k4[i], rr = r4[i];
-    S[4 * i] = fmaf(ww.x, S[4 * i], fmaf(kk.x, v, -bq.x * us));
-    S[4 * i + 1] = fmaf(ww.y, S[4 * i + 1], fmaf(kk.y, v, -bq.y * us));
-    S[4 * i + 2] = fmaf(ww.z, S[4 * i + 2], fmaf(kk.z, v, -bq.z * us));
-    S[4 * i + 3] = fmaf(ww.w, S[4 * i + 3], fmaf(kk.w, v, -bq.w * us));
+    const float4 bq = b4[i], rr = r4[i];
+    S[4 * i] = fmaf(-bq.x, us, e[4 * i]);
+    S[4 * i + 1] = fmaf(-bq.y, us, e[4 * i + 1]);
+    S[4 * i + 2] = fmaf(-bq.z, us, e[4 * i + 2]);
+    S[4 * i + 3] = fmaf(-bq.w, us, e[4 * i + 3]);
     a4[0] = fmaf(S[4 * i], rr.x, a4[0]);
     a4[1] = fmaf(S[4 * i + 1], rr.y, a4[1]);
     a4[2] = fmaf(S[4 * i + 2], rr.z, a4[2]);
@@ -324,7 +336,7 @@ __device__ __forceinline__ float delta_token(float (&S)[ROWS], const float *vecs
 }
 
 template <int DMAX, int LANES, bool VEC>
-__global__ void __launch_bounds__(DR_THREADS)
+__global__ void __launch_bounds__(DR_THREADS + 32)
 delta_rule_kernel(const float *__restrict__ proj, long long ld, int off_r, int off_k, int off_v,
                   const float *__restrict__ prep, float *__restrict__ state, float *__restrict__ out, long long ldo,
                   const int *__restrict__ seq_start, const int *__restrict__ seq_slot, int n_heads, int d) {
@@ -334,30 +346,34 @@ delta_rule_kernel(const float *__restrict__ proj, long long ld, int off_r, int o
   constexpr int VLEN = LANES * PAD;
   constexpr int SLOT = 5 * VLEN + COLS;              // floats of one token in the ring: w, b, u, k, r, then the CTA's columns of v
   constexpr int UNIT = VEC ? 4 : 1;                  // floats to a copy
-  constexpr int PER = (5 * DMAX / UNIT + COLS / UNIT + DR_THREADS - 1) / DR_THREADS;   // copies of a thread per token
+  constexpr int PER = (5 * DMAX / UNIT + COLS / UNIT + 31) / 32;   // copies of a loader lane per token
   constexpr int DR_STAGES = DR_STAGES_MAX * SLOT * 4 <= 48 * 1024 ? DR_STAGES_MAX : DR_STAGES_MAX / 2;
+  // Tokens go through the ring in groups of G: a group of copies is G tokens, DR_STAGES / G - 1 groups are in flight, and
+  // a barrier stands before every group (its copies have arrived for everyone, and everyone is done with the group whose
+  // place the next copies take).
+  constexpr int G = DR_STAGES / 4;
+  constexpr int GROUPS = DR_STAGES / G;
   __shared__ __align__(16) float ring[DR_STAGES][SLOT];
   grid_dependency_wait();
   const int b = blockIdx.x, hd = blockIdx.y;
-  const int tid = threadIdx.x, sub = tid % LANES, col = tid / LANES;
-  const int j0 = blockIdx.z * COLS, j = j0 + col;
+  const int tid = threadIdx.x;
+  const int j0 = blockIdx.z * COLS;
   const int start = seq_start[b], n = seq_start[b + 1] - start;
-  const bool live = j < d;
-  float S[ROWS];
-  float *sp = state + (((size_t)seq_slot[b] * n_heads + hd) * d + (live ? j : 0)) * d + sub * ROWS;
-#pragma unroll
-  for (int i = 0; i < ROWS; ++i) S[i] = (live && sub * ROWS + i < d) ? sp[i] : 0.f;
+  const int n_groups = (n + G - 1) / G;
   // rows beyond d of a lane's share are never copied: they stay zero, and so do the state's rows there
-  for (int i = tid; i < DR_STAGES * SLOT; i += DR_THREADS) (&ring[0][0])[i] = 0.f;
+  for (int i = tid; i < DR_STAGES * SLOT; i += DR_THREADS + 32) (&ring[0][0])[i] = 0.f;
+  __syncthreads();
 
-  // This thread's copies of a token, worked out once: where from (an offset into the token's prepared vectors, or
-  // into its row of the product, marked by bit 30) and where to (element i of a vector lies at (i / ROWS) * PAD + i % ROWS).
-  int from[PER], to[PER];
-  {
+  if (tid >= DR_THREADS) {
+    // ------------------------------------------------------------ the loader warp
+    // Its lanes' copies of a token, worked out once: where from (an offset into the token's prepared vectors, or into
+    // its row of the product, marked by bit 30) and where to (element i of a vector lies at (i / ROWS) * PAD + i % ROWS).
+    const int lane = tid - DR_THREADS;
+    int from[PER], to[PER];
     const int per_vec = d / UNIT, n_v = (min(COLS, d - j0) + UNIT - 1) / UNIT;
 #pragma unroll
     for (int e = 0; e < PER; ++e) {
-      const int idx = tid + e * DR_THREADS;
+      const int idx = lane + e * 32;
       from[e] = to[e] = -1;
       if (idx < 5 * per_vec) {
         const int which = idx / per_vec, i = (idx - which * per_vec) * UNIT;
@@ -369,46 +385,55 @@ delta_rule_kernel(const float *__restrict__ proj, long long ld, int off_r, int o
         to[e] = 5 * VLEN + i;
       }
     }
-  }
-  __syncthreads();
-  auto fetch = [&](int t) {
-    float *dst = ring[t % DR_STAGES];
-    const float *row = proj + (size_t)(start + t) * ld;
-    const float *pr = prep + ((size_t)(start + t) * n_heads + hd) * 3 * d;
+    auto fetch_group = [&](int p) {
+      for (int t = G * p; t < min(n, G * p + G); ++t) {
+        float *dst = ring[t % DR_STAGES];
+        const float *row = proj + (size_t)(start + t) * ld;
+        const float *pr = prep + ((size_t)(start + t) * n_heads + hd) * 3 * d;
 #pragma unroll
-    for (int e = 0; e < PER; ++e)
-      if (to[e] >= 0) {
-        const float *src = (from[e] & (1 << 30)) ? row + (from[e] & ~(1 << 30)) : pr + from[e];
-        if (VEC) cp_async16_cg(dst + to[e], src);
-        else cp_async4(dst + to[e], src);
+        for (int e = 0; e < PER; ++e)
+          if (to[e] >= 0) {
+            const float *src = (from[e] & (1 << 30)) ? row + (from[e] & ~(1 << 30)) : pr + from[e];
+            if (VEC) cp_async16_cg(dst + to[e], src);
+            else cp_async4(dst + to[e], src);
+          }
       }
-  };
+      cp_async_commit_group();
+    };
+    for (int p = 0; p < GROUPS - 1; ++p) fetch_group(p);
+    for (int p = 0; p < n_groups; ++p) {
+      cp_async_wait_group<GROUPS - 2>();              // group p has arrived
+      __syncthreads();                                // the other warps may read it; they are done with group p - 1
+      fetch_group(p + GROUPS - 1);                    // ... whose place these copies take
+    }
+    cp_async_wait_group<0>();
+    return;
+  }
+
+  // -------------------------------------------------------------- the two warps of the recurrence
+  const int sub = tid % LANES, col = tid / LANES;
+  const int j = j0 + col;
+  const bool live = j < d;
+  float S[ROWS];
+  float *sp = state + (((size_t)seq_slot[b] * n_heads + hd) * d + (live ? j : 0)) * d + sub * ROWS;
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) S[i] = (live && sub * ROWS + i < d) ? sp[i] : 0.f;
   auto token = [&](int t) {
     const float *slot = ring[t % DR_STAGES];
     const float acc = delta_token<ROWS, LANES>(S, slot + sub * PAD, VLEN, slot[5 * VLEN + col]);
     if (live && sub == 0) out[(size_t)(start + t) * ldo + (size_t)hd * d + j] = acc;
   };
-  // Tokens go through the ring in pairs: a group of copies is a pair, DR_STAGES / 2 - 1 pairs are in flight, and a
-  // barrier stands before every pair (its copies have arrived for everyone, and everyone is done with the pair
-  // whose place the next copies take).
-  constexpr int PAIRS = DR_STAGES / 2;
-  const int n_pairs = (n + 1) / 2;
-  auto fetch_pair = [&](int p) {
-    if (2 * p < n) fetch(2 * p);
-    if (2 * p + 1 < n) fetch(2 * p + 1);
-    cp_async_commit_group();
-  };
-  for (int p = 0; p < PAIRS - 1; ++p) fetch_pair(p);
-  for (int p = 0; p < n_pairs; ++p) {
-    cp_async_wait_group<PAIRS - 2>();
+  for (int p = 0; p < n_groups; ++p) {
     __syncthreads();
-    fetch_pair(p + PAIRS - 1);
-    token(2 * p);
-    if (2 * p + 1 < n) token(2 * p + 1);
+    if (G * p + G <= n) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) token(G * p + g);
+    } else {
+      for (int t = G * p; t < n; ++t) token(t);
+    }
   }
-  cp_async_wait_group<0>();
   // Only now may the next kernel's CTAs come onto the SMs: this kernel runs for as long as its longest sequence
-  // with two warps to a CTA, and a dependent let in at the start would sit beside them in its wait for all that time.
+  // with few warps to a CTA, and a dependent let in at the start would sit beside them in its wait for all that time.
   grid_dependents_launch();
   if (live)
 #pragma unroll
@@ -442,7 +467,7 @@ LLM_EXPORT int llm_delta_rule(const float *proj, long long ld, int off_r, int of
   // instead of 5.9 (measured).
 #define DR_GO2(DMAX, LANES, VEC)                                                                                        \
   llm_launch_after(delta_rule_kernel<DMAX, LANES, VEC>, dim3(n_seqs, n_heads, (d + DR_THREADS / LANES - 1) / (DR_THREADS / LANES)), \
-                   dim3(DR_THREADS), 0, stream, proj, ld, off_r, off_k, off_v, (const float *)prep, state, out, ldo, seq_start, \
+                   dim3(DR_THREADS + 32), 0, stream, proj, ld, off_r, off_k, off_v, (const float *)prep, state, out, ldo, seq_start, \
                    seq_slot, n_heads, d)
 #define DR_GO(DMAX, LANES)              \
   do {                                  \
