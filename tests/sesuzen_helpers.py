@@ -49,7 +49,7 @@ def config(vocab, width, eps, taps, cap, layers, loop=None, max_positions=512):
 # S4: one tap (no state of the convolution), more kept first tokens than a page holds, a window longer than
 #     any test sequence, a loop that runs once, all experts chosen, delta heads of 128 and a rank of 24.
 # S5: five taps, delta heads of 8 and of 32, full attention without a mask, an empty loop.
-# S6: no routed layer: in bfloat16 whole sequences are judged.
+# S6: no routed layer: in bfloat16 whole sequences are compared.
 # S7: widths that are multiples of 2 only (no 16-byte rows anywhere), delta heads of 10 with a rank of 3, two key/value
 #     heads for six query heads of 18 with values of 6, six taps, a cap that binds (logits beyond it).
 CONFIGS: Dict[str, dict] = {
@@ -158,7 +158,7 @@ def row_errors(got: torch.Tensor, ref: torch.Tensor) -> torch.Tensor:
 #   through another expert, and every later position sees that through the cache and the state;
 # * a head of the delta rule whose sum cancels to a small share of its terms (at a first token, where the head's
 #   result is v (k.r), when k.r is nearly nought: then even its sign): the norm behind it divides by what is left.
-# So in bfloat16 a sequence is judged up to its first close call or head that all but vanishes (``clear``: the number
+# So in bfloat16 a sequence is compared up to its first close call or head that all but vanishes (``clear``: the number
 # of leading positions before it) and must be finite after, and a position where less than 0.15 of a head survives
 # gets that much more room (``slack``).
 TOL = {"float32": 3e-5, "bfloat16": 5e-2}
@@ -195,4 +195,4 @@ def check_rows(got: torch.Tensor, ref: torch.Tensor, dtype: str, what: str, rout
         e = e[:clear]
         if e.numel() == 0:
             return
-    assert float(e.max()) < TOL[dtype], f"{what}: row error {float(e.max()):.3e} at position {int(e.argmax())} of {e.numel()} judged ({dtype})"
+    assert float(e.max()) < TOL[dtype], f"{what}: row error {float(e.max()):.3e} at position {int(e.argmax())} of {e.numel()} compared ({dtype})"

@@ -35,7 +35,7 @@ def plain(name, c, w, toks):
     return _refs[key][0]
 
 
-def judge(got, name, c, w, toks, dtype, what):
+def compare(got, name, c, w, toks, dtype, what):
     """Against the plain implementation; in bfloat16, up to the first position that hangs on a rounding."""
     ref = plain(name, c, w, toks)
     _, clear, slack = _refs[(name, tuple(toks))]
@@ -50,7 +50,7 @@ def test_whole_prompts(name, dtype):
     for i, n in enumerate([1, 2, 3, 5, 8, 11, 25, 41, 51, 64, 65, 73, 81, 130, 203]):
         toks = S.tokens(c, n, i)
         got = replay_batch(engine, [("r", toks, n)])["r"]
-        judge(got, name, c, w, toks, dtype, f"{name} whole {n}")
+        compare(got, name, c, w, toks, dtype, f"{name} whole {n}")
     assert engine.pages_in_use() == [0] * len(engine.pages_in_use())
 
 
@@ -63,7 +63,7 @@ def test_prompt_then_single_tokens_agrees_with_the_whole_prompt(name, dtype):
     for i, (n, n_prompt) in enumerate([(140, 100), (75, 35), (48, 1)]):
         toks = S.tokens(c, n, 20 + i)
         got = replay_batch(engine, [("r", toks, n_prompt)])["r"]
-        judge(got, name, c, w, toks, dtype, f"{name} {n_prompt} + {n - n_prompt} single tokens")
+        compare(got, name, c, w, toks, dtype, f"{name} {n_prompt} + {n - n_prompt} single tokens")
         if dtype == "float32":
             whole = replay_batch(engine, [("r", toks, n)])["r"]
             assert float(S.row_errors(got, whole).max()) < S.TOL[dtype], f"{name}: decoding differs from the whole prompt"
@@ -84,7 +84,7 @@ def test_portions_of_a_prompt(name, dtype):
             rows.append(torch.from_numpy(engine.step([StepItem(slot, toks[at:at + n], list(range(n)))])))
             at += n
         engine.close_sequence(slot)
-        judge(torch.cat(rows), name, c, w, toks, dtype, f"{name} portions {sizes[:4]}...")
+        compare(torch.cat(rows), name, c, w, toks, dtype, f"{name} portions {sizes[:4]}...")
     engine.cache_check()
 
 
@@ -105,7 +105,7 @@ def test_unequal_batches_against_each_request_alone(name, dtype):
             reqs.append((f"b{b}r{j}", S.tokens(c, total, 100 * b + j), p))
         got = replay_batch(engine, reqs)
         for rid, toks, p in reqs:
-            judge(got[rid], name, c, w, toks, dtype, f"{name} batch {b} {rid}")
+            compare(got[rid], name, c, w, toks, dtype, f"{name} batch {b} {rid}")
             if dtype == "float32" and b == 0:
                 single = replay_batch(alone, [(rid, toks, p)])[rid]
                 assert float(S.row_errors(got[rid], single).max()) < S.TOL[dtype], f"{name} {rid}: the batch changes the result"
@@ -120,7 +120,7 @@ def test_long_decoding(name, dtype):
     engine, c, w = setup(name, dtype)
     toks = S.tokens(c, 330, 77)
     got = replay_batch(engine, [("r", toks, 2)])["r"]
-    judge(got, name, c, w, toks, dtype, f"{name} long decoding")
+    compare(got, name, c, w, toks, dtype, f"{name} long decoding")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -128,8 +128,8 @@ def test_first_tokens_beside_a_long_neighbour(dtype):
     engine, c, w = setup("S1", dtype)
     short, long_ = S.tokens(c, 3, 5), S.tokens(c, 90, 6)
     both = replay_batch(engine, [("l", long_, 60), ("s", short, 1)])
-    judge(both["s"], "S1", c, w, short, dtype, "first tokens beside a long request")
-    judge(both["l"], "S1", c, w, long_, dtype, "long neighbour")
+    compare(both["s"], "S1", c, w, short, dtype, "first tokens beside a long request")
+    compare(both["l"], "S1", c, w, long_, dtype, "long neighbour")
 
 
 @pytest.mark.parametrize("name", NAMES)
@@ -159,7 +159,7 @@ def test_a_step_cut_into_launch_sequences(dtype):
     reqs = [("a", S.tokens(c, 150, 1), 150), ("b", S.tokens(c, 30, 2), 30)]
     got = replay_batch(engine, reqs)
     for rid, toks, _ in reqs:
-        judge(got[rid], "S2", c, w, toks, dtype, f"cut {rid}")
+        compare(got[rid], "S2", c, w, toks, dtype, f"cut {rid}")
 
 
 @pytest.mark.parametrize("name", NAMES)

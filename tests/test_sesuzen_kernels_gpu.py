@@ -318,7 +318,7 @@ def test_norm_per_head_weight_and_gate(dtype, H, dv):
 @pytest.mark.parametrize("dtype,grouped", [("float32", False), ("bfloat16", False), ("bfloat16", True), ("bfloat16", "tc")])
 @pytest.mark.parametrize("T,E,top,width,ff", [(37, 5, 2, 72, 24), (200, 8, 4, 128, 64), (3, 3, 3, 64, 40), (700, 4, 1, 64, 136)])
 def test_gated_experts_with_the_choice_given(dtype, grouped, T, E, top, width, ff):
-    """down(silu(gate x) * up x) of the chosen experts, the choice given (so that bfloat16 is judged on the products
+    """down(silu(gate x) * up x) of the chosen experts, the choice given (so that bfloat16 is compared on the products
     alone): rows on the CUDA cores, sorted tiles on mma.sync and on tcgen05."""
     from libllm_b200.csrc import ops
     g = torch.Generator().manual_seed(T + E)
